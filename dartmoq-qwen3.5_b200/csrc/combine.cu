@@ -1,0 +1,91 @@
+// Deterministic combine of the routed rows back into token order, the
+// group-first relayout kernel, and the small C-ABI utility entry points.
+#include "common.cuh"
+
+namespace {
+
+// y[t] = sum over the token's slots (then the shared row) of dn[row], fp32, fixed order.
+// Replaces final_hidden_states.index_add_(0, pool_tokens, dn)
+// (quantization/wxa16/bit_partitioned_moe.py:966), whose atomic order is not fixed.
+__global__ void combine_kernel(const int32_t* __restrict__ row_of, const uint16_t* __restrict__ dn,
+                               int T, int top_k, int has_shared, int hidden, void* y, int y_is_bf16) {
+  const int chunks = hidden / 8;
+  const long long total = (long long)T * chunks;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / chunks), c = (int)(i % chunks);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const int n_src = top_k + (has_shared ? 1 : 0);
+    for (int s = 0; s < n_src; ++s) {
+      const int row = (s < top_k) ? row_of[(size_t)t * top_k + s] : row_of[(size_t)T * top_k + t];
+      if (row < 0) continue;
+      const uint4 v = *reinterpret_cast<const uint4*>(dn + (size_t)row * hidden + c * 8);
+      const uint16_t* u = reinterpret_cast<const uint16_t*>(&v);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] += bf16_bits_to_float(u[q]);
+    }
+    __align__(16) uint16_t o[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      o[q] = y_is_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(acc[q])) : __half_as_ushort(__float2half_rn(acc[q]));
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(y) + (size_t)t * hidden + c * 8) =
+        *reinterpret_cast<const uint4*>(o);
+  }
+}
+
+// (N, G*bpg) -> (G, N, bpg), 16-byte granules
+__global__ void group_first_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int N, int G, int bpg) {
+  const int per_row = bpg / 16;
+  const long long total = (long long)N * G * per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int q = (int)(i % per_row);
+    const long long ng = i / per_row;
+    const int n = (int)(ng % N), g = (int)(ng / N);
+    const uint4 v = *reinterpret_cast<const uint4*>(src + ((size_t)n * G + g) * bpg + q * 16);
+    *reinterpret_cast<uint4*>(dst + ((size_t)g * N + n) * bpg + q * 16) = v;
+  }
+}
+
+}  // namespace
+
+extern "C" int dmoq_combine(const dmoq_route_t* route, const uint16_t* dn, int32_t hidden,
+                            void* y, int32_t y_is_bf16, void* stream) {
+  DMOQ_CHECK_ARG(route && dn && y && route->row_of);
+  DMOQ_CHECK_ARG(hidden > 0 && hidden % 8 == 0);
+  if (route->T == 0) return DMOQ_OK;
+  const long long total = (long long)route->T * (hidden / 8);
+  long long blocks = (total + 255) / 256;
+  const long long cap = 8LL * dmoq_sm_count();
+  if (blocks > cap) blocks = cap;
+  combine_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      route->row_of, dn, route->T, route->top_k, route->has_shared, hidden, y, y_is_bf16);
+  return dmoq_launch_status();
+}
+
+extern "C" int dmoq_convert_group_first(const uint8_t* row_major, int32_t N, int32_t K, int32_t bit,
+                                        uint8_t* group_first, void* stream) {
+  DMOQ_CHECK_ARG(row_major && group_first);
+  DMOQ_CHECK_ARG(bit == 1 || bit == 2 || bit == 4 || bit == 8);
+  DMOQ_CHECK_ARG(N > 0 && K > 0 && K % DMOQ_GROUP == 0);
+  const int G = K / DMOQ_GROUP, bpg = 16 * bit;
+  const long long total = (long long)N * G * (bpg / 16);
+  long long blocks = (total + 255) / 256;
+  const long long cap = 16LL * dmoq_sm_count();
+  if (blocks > cap) blocks = cap;
+  group_first_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(row_major, group_first, N, G, bpg);
+  return dmoq_launch_status();
+}
+
+extern "C" int dmoq_version(void) { return DMOQ_VERSION; }
+
+extern "C" const char* dmoq_strerror(int code) {
+  switch (code) {
+    case DMOQ_OK: return "ok";
+    case DMOQ_EINVAL: return "invalid argument";
+    case DMOQ_ELAUNCH: return "CUDA launch or attribute call failed";
+    case DMOQ_ESIZE: return "size exceeds a stated maximum or a buffer is too small";
+    case DMOQ_EDEVICE: return "no usable CUDA device or device symbol set-up failed";
+    default: return "unknown dmoq error";
+  }
+}

@@ -1,0 +1,248 @@
+// Device-side routing tables: histogram -> scan -> stable counting sort, the
+// per-pool tile lists and the activation-table row maps.  No host round trip.
+//
+// Stands in for argsort + bincount(...).cpu().cumsum() and the Python pool /
+// expert_info / block_info builders of the reference
+// (quantization/wxa16/bit_partitioned_moe.py:1125-1138, :1014-1057;
+//  turboquant_utils/triton_kernels_a8.py:938).
+#include "common.cuh"
+
+namespace {
+
+constexpr int kChunk = 1024;  // flat (token, slot) entries per chunk
+
+struct RouteArgs {
+  dmoq_route_t r;
+  const int64_t* topk_idx;
+  const float* topk_w;
+  const float* shared_w;
+  int32_t* hist;        // (n_chunks, E) chunk histograms, turned into chunk offsets in place
+  int32_t* pool_row0;   // (E + has_shared) first activation-table row of each expert inside its pool
+  int32_t n_flat;       // T * top_k
+  int32_t n_chunks;
+};
+
+// --- phase 1: per-chunk histogram ------------------------------------------------------
+__device__ void chunk_histogram(const RouteArgs& a, int chunk, int32_t* s_hist) {
+  const int E = a.r.E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) s_hist[e] = 0;
+  __syncthreads();
+  const int lo = chunk * kChunk;
+  const int hi = min(lo + kChunk, a.n_flat);
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    long long e = a.topk_idx[i];
+    if (e >= 0 && e < E) atomicAdd(&s_hist[(int)e], 1);
+  }
+  __syncthreads();
+}
+
+// --- phase 2: scans, pool bookkeeping, tile lists (one block) ---------------------------
+__device__ void scan_and_tiles(const RouteArgs& a, int32_t* s_count /* E_tot+1 ints */) {
+  const int E = a.r.E;
+  const int E_tot = E + a.r.has_shared;
+  const int P = a.r.n_pools;
+  __shared__ int32_t s_tile_base[DMOQ_MAX_POOLS];
+
+  // rows per expert; chunk histograms become exclusive chunk offsets
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < a.n_chunks; ++c) {
+      int v = a.hist[(size_t)c * E + e];
+      a.hist[(size_t)c * E + e] = run;
+      run += v;
+    }
+    s_count[e] = run;
+  }
+  if (threadIdx.x == 0 && a.r.has_shared) s_count[E] = a.r.T;
+  __syncthreads();
+
+  if (threadIdx.x == 0) {
+    int32_t pool_rows[DMOQ_MAX_POOLS], pool_tiles[DMOQ_MAX_POOLS];
+    for (int p = 0; p < DMOQ_MAX_POOLS; ++p) pool_rows[p] = pool_tiles[p] = 0;
+    int run = 0;
+    for (int e = 0; e < E_tot; ++e) {
+      int n = s_count[e];
+      a.r.expert_rows[e] = run;
+      run += n;
+      int p = a.r.expert_pool[e];
+      if (p >= 0 && p < P) {
+        a.pool_row0[e] = pool_rows[p];
+        pool_rows[p] += n;
+        pool_tiles[p] += (n + a.r.tile_m - 1) / a.r.tile_m;
+      } else {
+        a.pool_row0[e] = 0;
+      }
+    }
+    a.r.expert_rows[E_tot] = run;
+    int src = 0, tb = 0;
+    for (int p = 0; p < DMOQ_MAX_POOLS; ++p) {
+      s_tile_base[p] = tb;
+      a.r.pool_rows[p] = pool_rows[p];
+      a.r.pool_src_base[p] = src;
+      a.r.n_tiles[p] = pool_tiles[p];
+      a.r.n_tiles[DMOQ_MAX_POOLS + p] = tb;
+      if (p < P && !a.r.pool_hoisted[p]) src += pool_rows[p];
+      tb += pool_tiles[p];
+    }
+  }
+  __syncthreads();
+
+  // tile lists: pool p's tiles are contiguous from s_tile_base[p], experts in index order.
+  // Each thread walks the experts before its own to find its first tile slot.
+  for (int e = threadIdx.x; e < E_tot; e += blockDim.x) {
+    int p = a.r.expert_pool[e];
+    if (p < 0 || p >= P) continue;
+    int n = s_count[e];
+    if (n == 0) continue;
+    int slot = s_tile_base[p];
+    for (int q = 0; q < e; ++q)
+      if (a.r.expert_pool[q] == p) slot += (s_count[q] + a.r.tile_m - 1) / a.r.tile_m;
+    int row0 = a.r.expert_rows[e];
+    for (int m = 0; m < n; m += a.r.tile_m, ++slot) {
+      if (slot >= a.r.tile_cap) break;
+      DmoqTile t{e, row0 + m, min(a.r.tile_m, n - m), p};
+      reinterpret_cast<DmoqTile*>(a.r.tiles)[slot] = t;
+    }
+  }
+}
+
+// --- phase 3: stable placement of one chunk (one warp) ----------------------------------
+__device__ void place_chunk(const RouteArgs& a, int chunk, int32_t* s_running) {
+  const int E = a.r.E;
+  const int lane = threadIdx.x & 31;
+  for (int e = lane; e < E; e += 32) s_running[e] = 0;
+  __syncwarp();
+  const int lo = chunk * kChunk;
+  const int hi = min(lo + kChunk, a.n_flat);
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    long long e64 = (i < hi) ? a.topk_idx[i] : -1;
+    const bool ok = (e64 >= 0 && e64 < E);
+    const int e = ok ? (int)e64 : -1 - lane;  // invalid lanes get unique keys
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int before = __popc(peers & ((1u << lane) - 1));
+    int start = 0;
+    if (ok) start = s_running[e];
+    __syncwarp();
+    if (ok && before == 0) s_running[e] = start + __popc(peers);
+    __syncwarp();
+    if (i < hi) {
+      if (!ok) {
+        a.r.row_of[i] = -1;
+        continue;
+      }
+      const int within = a.hist[(size_t)chunk * E + e] + start + before;
+      const int pos = a.r.expert_rows[e] + within;
+      const int tok = i / a.r.top_k;
+      const int p = a.r.expert_pool[e];
+      a.r.sorted_tokens[pos] = tok;
+      a.r.sorted_weights[pos] = a.topk_w[i];
+      if (p < 0 || p >= a.r.n_pools) {
+        a.r.row_of[i] = -1;  // expert without weights contributes nothing
+        a.r.a_row[pos] = 0;
+      } else {
+        a.r.row_of[i] = pos;
+        if (a.r.pool_hoisted[p]) {
+          a.r.a_row[pos] = tok;
+        } else {
+          const int tr = a.pool_row0[e] + within;
+          a.r.a_row[pos] = tr;
+          a.r.pool_src[a.r.pool_src_base[p] + tr] = tok;
+        }
+      }
+    }
+  }
+}
+
+__device__ void place_shared(const RouteArgs& a, int t0, int t1) {
+  const int E = a.r.E;
+  const int row0 = a.r.expert_rows[E];
+  const int p = a.r.expert_pool[E];
+  for (int t = t0 + threadIdx.x; t < t1; t += blockDim.x) {
+    const int pos = row0 + t;
+    a.r.sorted_tokens[pos] = t;
+    a.r.sorted_weights[pos] = a.shared_w ? a.shared_w[t] : 1.0f;
+    a.r.row_of[a.n_flat + t] = (p >= 0 && p < a.r.n_pools) ? pos : -1;
+    a.r.a_row[pos] = t;
+  }
+}
+
+__global__ void route_hist_kernel(RouteArgs a) {
+  extern __shared__ int32_t s_dyn[];
+  chunk_histogram(a, blockIdx.x, s_dyn);
+  for (int e = threadIdx.x; e < a.r.E; e += blockDim.x) a.hist[(size_t)blockIdx.x * a.r.E + e] = s_dyn[e];
+}
+
+__global__ void route_scan_kernel(RouteArgs a) {
+  extern __shared__ int32_t s_dyn[];
+  scan_and_tiles(a, s_dyn);
+}
+
+__global__ void route_place_kernel(RouteArgs a) {
+  extern __shared__ int32_t s_dyn[];
+  if ((int)blockIdx.x < a.n_chunks) {
+    place_chunk(a, blockIdx.x, s_dyn);
+  } else if (a.r.has_shared) {
+    const int b = blockIdx.x - a.n_chunks;
+    place_shared(a, b * kChunk, min((b + 1) * kChunk, a.r.T));
+  }
+}
+
+// Small problems (one chunk): everything in a single block.
+__global__ void route_fused_kernel(RouteArgs a) {
+  extern __shared__ int32_t s_dyn[];  // [0, E): histogram / running, [E, 2E+2): counts
+  int32_t* s_hist = s_dyn;
+  int32_t* s_count = s_dyn + a.r.E;
+  chunk_histogram(a, 0, s_hist);
+  for (int e = threadIdx.x; e < a.r.E; e += blockDim.x) a.hist[e] = s_hist[e];
+  __syncthreads();
+  scan_and_tiles(a, s_count);
+  __syncthreads();
+  if (threadIdx.x < 32) place_chunk(a, 0, s_hist);
+  if (a.r.has_shared) place_shared(a, 0, a.r.T);
+}
+
+}  // namespace
+
+extern "C" size_t dmoq_route_workspace_bytes(int32_t T, int32_t top_k, int32_t E) {
+  if (T < 0 || top_k <= 0 || E <= 0) return 0;
+  size_t n_chunks = ((size_t)T * top_k + kChunk - 1) / kChunk;
+  if (n_chunks == 0) n_chunks = 1;
+  return (n_chunks * (size_t)E + (size_t)E + 1) * sizeof(int32_t);
+}
+
+extern "C" int dmoq_route_build(const dmoq_route_t* route, const int64_t* topk_idx, const float* topk_w,
+                                const float* shared_w, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  DMOQ_CHECK_ARG(route && topk_idx && topk_w && workspace);
+  const dmoq_route_t& r = *route;
+  DMOQ_CHECK_ARG(r.T >= 0 && r.top_k > 0 && r.E > 0 && r.E <= 4096 && r.tile_m > 0);
+  DMOQ_CHECK_ARG(r.n_pools >= 0 && r.n_pools <= DMOQ_MAX_POOLS);
+  DMOQ_CHECK_ARG(r.expert_pool && r.expert_rank && r.expert_rows && r.sorted_tokens && r.sorted_weights);
+  DMOQ_CHECK_ARG(r.row_of && r.a_row && r.pool_rows && r.pool_src && r.pool_src_base && r.tiles && r.n_tiles);
+  DMOQ_CHECK_ARG(r.pool_hoisted);
+  if (workspace_bytes < dmoq_route_workspace_bytes(r.T, r.top_k, r.E)) return DMOQ_ESIZE;
+
+  RouteArgs a;
+  a.r = r;
+  a.topk_idx = topk_idx;
+  a.topk_w = topk_w;
+  a.shared_w = shared_w;
+  a.n_flat = r.T * r.top_k;
+  a.n_chunks = dmoq_ceil_div(a.n_flat, kChunk);
+  if (a.n_chunks == 0) a.n_chunks = 1;
+  a.hist = static_cast<int32_t*>(workspace);
+  a.pool_row0 = a.hist + (size_t)a.n_chunks * r.E;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t e_bytes = (size_t)r.E * sizeof(int32_t);
+
+  if (a.n_chunks == 1 && (!r.has_shared || r.T <= 4 * kChunk)) {
+    route_fused_kernel<<<1, 1024, 2 * e_bytes + 16, s>>>(a);
+    return dmoq_launch_status();
+  }
+  route_hist_kernel<<<a.n_chunks, 256, e_bytes, s>>>(a);
+  route_scan_kernel<<<1, 1024, e_bytes + 16, s>>>(a);
+  const int shared_blocks = r.has_shared ? dmoq_ceil_div(r.T, kChunk) : 0;
+  route_place_kernel<<<a.n_chunks + shared_blocks, 32, e_bytes, s>>>(a);
+  return dmoq_launch_status();
+}

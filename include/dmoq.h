@@ -1,0 +1,199 @@
+/*
+ * dmoq.h - C ABI of libdmoq: the sm_100a kernels behind the mixed-bit
+ * codebook-quantized MoE expert layer.
+ *
+ * The reference project is pure Python and launches Triton kernels through
+ * Python wrappers; it has no FFI.  Each entry point below replaces one of
+ * those wrappers (or a chain of torch ops around them) and cites it by the
+ * file's path inside the reference project.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the name ends in _host
+ *   - the caller owns all memory (inputs, outputs, workspaces); nothing here
+ *     allocates or frees device memory
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it
+ *     and the call returns without synchronising
+ *   - return value: DMOQ_OK or a negative DMOQ_E* code; dmoq_strerror() names it
+ *   - "rows" are routed (token, expert) pairs sorted by expert; the shared
+ *     expert, when present, is expert index E with one row per token
+ */
+#ifndef DMOQ_H
+#define DMOQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DMOQ_VERSION 100
+
+enum {
+  DMOQ_OK = 0,
+  DMOQ_EINVAL = -1,   /* bad argument (null pointer, unsupported size/bit/mode) */
+  DMOQ_ELAUNCH = -2,  /* the CUDA runtime refused a launch or an attribute change */
+  DMOQ_ESIZE = -3,    /* a size exceeds a stated maximum */
+  DMOQ_EDEVICE = -4   /* no usable device / symbol set-up failed */
+};
+
+/* activation modes: what the activations are quantised to before the GEMMs */
+enum { DMOQ_A16 = 0, DMOQ_A8 = 1, DMOQ_FP8 = 2, DMOQ_FP4 = 3 };
+
+/* GEMM epilogues */
+enum {
+  DMOQ_EPI_SILU = 0,     /* tile = [gate | up]; store silu(gate)*up as fp16 (I columns)   */
+  DMOQ_EPI_WEIGHTED = 1, /* store bf16(bf16(fp16(acc)) * row_weight)  (down projection)   */
+  DMOQ_EPI_PLAIN = 2     /* store fp16(acc)                                                */
+};
+
+#define DMOQ_GROUP 128      /* quantisation group = rotation block, fixed by the format */
+#define DMOQ_MAX_POOLS 8
+
+/*
+ * One bit pool = all experts stored at the same bit width (plus, optionally,
+ * a one-member pool for the shared expert).  Layouts are the reference's
+ * "group-first" runtime layout (turboquant_utils/triton_kernels.py:1042):
+ *   gu_idx  (G_h, n_members*2*inter, 16*bit) bytes     gu_norm (G_h, n_members*2*inter) fp16
+ *   dn_idx  (n_members*inter/128, hidden, 16*bit)      dn_norm (n_members*inter/128, hidden) fp16
+ * norms already carry 1/sqrt(128) (and the e2m1 residual in FP4 mode), as the
+ * reference prepares them (quantization/wxa16/bit_partitioned_moe.py:203,
+ * quantization/wxfp4/bit_partitioned_moe.py:98).
+ * Member `rank` owns gu rows [2*inter*rank, 2*inter*(rank+1)) (gate rows first,
+ * then up rows) and dn groups [rank*inter/128, (rank+1)*inter/128)
+ * (bit_partitioned_moe.py:120-166).
+ */
+typedef struct dmoq_pool {
+  int32_t bit;            /* 1, 2, 4 or 8 */
+  int32_t mode;           /* DMOQ_A16/A8/FP8/FP4 for this pool (the FP4 module runs bit 2 as A8) */
+  int32_t n_members;
+  int32_t inter;          /* intermediate size of every member (multiple of 128) */
+  int32_t hoisted;        /* 1: activations of ALL tokens are rotated+quantised once (table row = token) */
+  int32_t act_cap_rows;   /* capacity (rows) of this pool's activation-code table */
+  const uint8_t* gu_idx;
+  const uint16_t* gu_norm;
+  const uint8_t* dn_idx;
+  const uint16_t* dn_norm;
+  const void* gu_lut;     /* 2^bit entries: fp16 (A16), int8 (A8), e4m3 (FP8), e2m1 nibble (FP4); */
+  const void* dn_lut;     /* ignored when identity_lut != 0                                          */
+  int32_t identity_lut;   /* 8-bit uniform codebook: weight = index-128 (quantization/wxa8/linear.py:64) */
+  int32_t gu_e0, dn_e0;   /* FP4: weight block exponent E0 (triton_kernels_fp4.py:74) */
+  float gu_act_scale;     /* folded into stored activation scales: cb_step (A8), cb_scale (FP8), else 1 */
+  float dn_act_scale;
+  const uint16_t* gu_rot; /* (G_h, 128, 128) fp16 rotations, seed 42+bit + g*128            */
+  const uint16_t* dn_rot; /* (n_members*inter/128, 128, 128) fp16, seed 42+bit+1000 + j*128 */
+  /* per-forward buffers owned by the caller */
+  void* act_codes;        /* gate_up-side activation codes, act_cap_rows rows (see dmoq_rotate_quant) */
+  void* act_scales;
+} dmoq_pool_t;
+
+/* Routing tables produced by dmoq_route_build; all int32 unless noted. */
+typedef struct dmoq_route {
+  int32_t T, top_k, E;        /* E routed experts; expert index E is the shared expert when has_shared */
+  int32_t has_shared;
+  int32_t tile_m;             /* rows per tile in the tile lists */
+  int32_t n_pools;
+  const int32_t* expert_pool; /* (E+has_shared) static: pool index of each expert, -1 = unused */
+  const int32_t* expert_rank; /* (E+has_shared) static: member rank inside its pool           */
+  int32_t* expert_rows;       /* (E+has_shared+1) exclusive prefix of rows per expert          */
+  int32_t* sorted_tokens;     /* (R) token of each row, R = T*top_k + has_shared*T             */
+  float* sorted_weights;      /* (R) routing weight of each row                                */
+  int32_t* row_of;            /* (R) row of flat (token, slot) pair; shared rows follow        */
+  int32_t* a_row;             /* (R) row of the pool's activation-code table feeding this row  */
+  int32_t* pool_rows;         /* (DMOQ_MAX_POOLS) rows routed to each pool                     */
+  int32_t* pool_src;          /* (R) for non-hoisted pools: token of each compact table row,
+                                 pool p's list starts at pool_src_base[p]                      */
+  int32_t* pool_src_base;     /* (DMOQ_MAX_POOLS) */
+  int32_t* tiles;             /* (tile_cap, 4): expert, first row, row count, pool             */
+  int32_t* n_tiles;           /* (DMOQ_MAX_POOLS+1) tiles per pool, then exclusive prefix base  */
+  int32_t tile_cap;
+  const int32_t* pool_hoisted;/* (DMOQ_MAX_POOLS) static copy of dmoq_pool_t.hoisted           */
+} dmoq_route_t;
+
+int dmoq_version(void);
+const char* dmoq_strerror(int code);
+
+/* bytes of scratch dmoq_route_build needs for (T, top_k, E) */
+size_t dmoq_route_workspace_bytes(int32_t T, int32_t top_k, int32_t E);
+
+/*
+ * Histogram / scan / stable counting sort of the router's top-k choices, the
+ * per-pool tile lists and the activation-table row maps, all on the device.
+ * Replaces argsort + bincount(...).cpu() + the Python pool/block-info builders
+ * (quantization/wxa16/bit_partitioned_moe.py:1125-1138, :1014-1057,
+ * turboquant_utils/triton_kernels_a8.py:938).  Rows of one expert are ordered
+ * by token index, so the result is deterministic.
+ *   topk_idx (T, top_k) int64, topk_w (T, top_k) fp32, shared_w (T) fp32 or NULL
+ */
+int dmoq_route_build(const dmoq_route_t* route, const int64_t* topk_idx, const float* topk_w,
+                     const float* shared_w, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Group rotation fused with activation quantisation
+ * (turboquant_utils/triton_kernels_a8.py:429 int8, triton_kernels_fp8.py:128 e4m3,
+ *  triton_kernels_fp4.py:1036 e2m1+e8m0; rotation.py:176 for the unquantised A16 case).
+ *   x        (n_src_rows, K) bf16 or fp16 (src_is_bf16), K = G*128
+ *   rot      rotation stack, fp16; matrix used for (row, group g) is
+ *            rot[(rot_row_group0 ? rot_row_group0[row] : 0) + g]
+ *   src_row  optional (n_rows) int32: output row i reads x[src_row[i]]; NULL = identity
+ *   n_rows_dev optional device int32: actual row count (<= n_rows), read on the device
+ *   codes    A16: (n_rows, K) fp16 rotated values;  A8: int8;  FP8: e4m3 bytes;
+ *            FP4: (n_rows, K/2) bytes, even k in the low nibble (row-major, not transposed)
+ *   scales   A8/FP8: (n_rows, G) fp16 = scale*extra_scale;  FP4: (n_rows, K/32) e8m0 bytes; A16: unused
+ * Each output row's accumulation is a sequential fp32 FMA chain over k = 0..127,
+ * which makes the integer codes reproducible bit for bit on a CPU.
+ */
+int dmoq_rotate_quant(int32_t mode, const void* x, int32_t src_is_bf16, int32_t K,
+                      const uint16_t* rot, const int32_t* rot_row_group0,
+                      const int32_t* src_row, int32_t n_rows, const int32_t* n_rows_dev,
+                      float extra_scale, void* codes, void* scales, void* stream);
+
+/*
+ * Down-side rotate+quantise of the SiLU output, one rotation stack per expert
+ * (quantization/wxa8/bit_partitioned_moe.py:346-358): rows are taken from the
+ * tile lists of `route`, the rotation of row r / group g is
+ * pool.dn_rot[rank(expert(r))*inter/128 + g].
+ *   act (R, inter) fp16 -> codes/scales laid out as in dmoq_rotate_quant with K = inter
+ */
+int dmoq_rotate_quant_down(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t pool_index,
+                           const uint16_t* act, void* codes, void* scales, void* stream);
+
+/*
+ * Grouped LUT-dequant GEMM over one pool's tile list.
+ *   gate_up: out[r, i] = silu(G[r,i]) * U[r,i],  [G|U][r, n] = sum_g norm[g,n] * xs[r,g] * sum_k a[r,g,k]*LUT[idx[g,n,k]]
+ *            replaces *_matmul_merged_rows_gf + F.silu*up
+ *            (triton_kernels.py:1482, triton_kernels_a8.py:959, triton_kernels_fp8.py:641,
+ *             triton_kernels_fp4.py:740; quantization/wxa16/bit_partitioned_moe.py:925-931)
+ *   down:    out[r, h] = bf16(bf16(fp16(D[r,h])) * w[r])
+ *            replaces *_matmul_merged_in_features_gf + dn.mul_(w)
+ *            (triton_kernels.py:1554, triton_kernels_a8.py:1017, triton_kernels_fp8.py:699,
+ *             triton_kernels_fp4.py:811; quantization/wxa16/bit_partitioned_moe.py:960-966)
+ * `a_codes`/`a_scales` are the pool's activation table; rows are gathered through
+ * route->a_row (gate_up) or taken at the row's own index (down).
+ * `partials` (optional, A8 only): int32 (R, N, G) per-group integer sums for parity checks.
+ */
+int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t pool_index,
+                      int32_t is_down, int32_t epilogue, int32_t hidden,
+                      const void* a_codes, const void* a_scales,
+                      void* out, int32_t out_stride, int32_t* partials, void* stream);
+
+/*
+ * Deterministic combine: y[t] = bf16( sum_slots dn[row_of[t*top_k+slot]] (+ dn[shared row of t]) ),
+ * accumulated in fp32 in slot order.  Replaces final_hidden_states.index_add_
+ * (quantization/wxa16/bit_partitioned_moe.py:966) and the shared-expert add (:1101-1106).
+ *   dn (R, hidden) bf16 already multiplied by the routing weight;  y (T, hidden) bf16 or fp16
+ */
+int dmoq_combine(const dmoq_route_t* route, const uint16_t* dn, int32_t hidden,
+                 void* y, int32_t y_is_bf16, void* stream);
+
+/*
+ * Runtime layout conversion (N, K*bit/8) row-major bytes -> (K/128, N, 16*bit) on the device
+ * (turboquant_utils/triton_kernels.py:1042).
+ */
+int dmoq_convert_group_first(const uint8_t* row_major, int32_t N, int32_t K, int32_t bit,
+                             uint8_t* group_first, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DMOQ_H */
