@@ -33,7 +33,7 @@ struct GemmArgs {
   int identity_lut, e0;
   const uint8_t* a_codes;
   const uint8_t* a_scales;
-  int K;                        // columns of the activation table (hidden or inter)
+  int a_stride;                 // row pitch (elements) of the activation-code table
   void* out;
   int out_stride;
   int32_t* partials;
@@ -172,14 +172,14 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
       // activation codes
       if (MODE == DMOQ_FP4) {
         const int ar = s_arow[bj];
-        if (ar >= 0) raw_a4 = *reinterpret_cast<const uint4*>(a.a_codes + (size_t)ar * (a.K / 2) + g * (kG / 2) + bq * 16);
+        if (ar >= 0) raw_a4 = *reinterpret_cast<const uint4*>(a.a_codes + (size_t)ar * (a.a_stride / 2) + g * (kG / 2) + bq * 16);
         else raw_a4 = make_uint4(0, 0, 0, 0);
       } else {
         constexpr int CH = ROWB / 16;  // chunks per row
         for (int c = tid; c < kBM * CH; c += kThreads) {
           const int r = c / CH, ch = c % CH;
           const int ar = s_arow[r];
-          const uint8_t* src = a.a_codes + ((size_t)(ar < 0 ? 0 : ar) * a.K + (size_t)g * kG) * ES + ch * 16;
+          const uint8_t* src = a.a_codes + ((size_t)(ar < 0 ? 0 : ar) * a.a_stride + (size_t)g * kG) * ES + ch * 16;
           cp_async16_zfill(s_a + buf * TILEB + swz<ROWB>(r, ch), src, ar >= 0);
         }
       }
@@ -200,9 +200,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
         const int ar = s_arow[tid];
         float* rs = s_rs + (buf * kBM + tid) * 4;
         if (MODE == DMOQ_A8 || MODE == DMOQ_FP8) {
-          rs[0] = ar >= 0 ? __half2float(reinterpret_cast<const __half*>(a.a_scales)[(size_t)ar * (a.K / kG) + g]) : 0.f;
+          rs[0] = ar >= 0 ? __half2float(reinterpret_cast<const __half*>(a.a_scales)[(size_t)ar * (a.a_stride / kG) + g]) : 0.f;
         } else if (MODE == DMOQ_FP4) {
-          uint32_t e4 = ar >= 0 ? *reinterpret_cast<const uint32_t*>(a.a_scales + (size_t)ar * (a.K / 32) + g * 4) : 0u;
+          uint32_t e4 = ar >= 0 ? *reinterpret_cast<const uint32_t*>(a.a_scales + (size_t)ar * (a.a_stride / 32) + g * 4) : 0u;
 #pragma unroll
           for (int q = 0; q < 4; ++q)
             rs[q] = ar >= 0 ? ldexpf(1.0f, (int)((e4 >> (8 * q)) & 255) - 127 + a.e0) : 0.f;
@@ -346,6 +346,24 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
           *reinterpret_cast<uint4*>(out + (size_t)(tile.row0 + r) * a.out_stride + nb * 64 + ch * 8) =
               *reinterpret_cast<const uint4*>(s_out + r * 64 + ch * 8);
       }
+    } else if (EPI == DMOQ_EPI_PLAIN && !a.is_down) {
+      // un-fused gate_up output (R, 2*inter) fp16: column j of the tile is gate (even) / up (odd)
+      __half* out = reinterpret_cast<__half*>(a.out);
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int r = wm * 32 + mt * 16 + (lane >> 2) + h * 8;
+          if (r >= tile.rows) continue;
+#pragma unroll
+          for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              const int c = wn * 32 + nt * 8 + (lane & 3) * 2 + q;
+              const int n = (c & 1) * a.inter + nb * (kBN / 2) + (c >> 1);
+              out[(size_t)(tile.row0 + r) * a.out_stride + n] = __float2half_rn(total[mt][nt][h * 2 + q]);
+            }
+        }
     } else {
       uint16_t* s_out = reinterpret_cast<uint16_t*>(smem);  // 128 x 128
 #pragma unroll
@@ -429,7 +447,7 @@ int launch_bit(const GemmArgs& a, int bit, int epi, int work_cap, cudaStream_t s
 
 extern "C" int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t pool_index,
                                  int32_t is_down, int32_t epilogue, int32_t hidden,
-                                 const void* a_codes, const void* a_scales,
+                                 const void* a_codes, const void* a_scales, int32_t a_stride,
                                  void* out, int32_t out_stride, int32_t* partials, void* stream) {
   DMOQ_CHECK_ARG(route && pools_host && a_codes && out);
   DMOQ_CHECK_ARG(pool_index >= 0 && pool_index < route->n_pools);
@@ -438,7 +456,7 @@ extern "C" int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* p
   DMOQ_CHECK_ARG(p.inter > 0 && p.inter % kG == 0 && hidden > 0 && hidden % kG == 0);
   DMOQ_CHECK_ARG(p.identity_lut || (is_down ? p.dn_lut : p.gu_lut));
   DMOQ_CHECK_ARG(p.mode == DMOQ_A16 || a_scales);
-  DMOQ_CHECK_ARG((epilogue == DMOQ_EPI_SILU) == (!is_down));
+  DMOQ_CHECK_ARG(!(epilogue == DMOQ_EPI_SILU && is_down) && !(epilogue == DMOQ_EPI_WEIGHTED && !is_down));
   DMOQ_CHECK_ARG(out_stride % 8 == 0);
   if (p.bit == 8 && p.mode == DMOQ_FP4) return DMOQ_EINVAL;
 
@@ -460,7 +478,8 @@ extern "C" int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* p
   a.e0 = is_down ? p.dn_e0 : p.gu_e0;
   a.a_codes = static_cast<const uint8_t*>(a_codes);
   a.a_scales = static_cast<const uint8_t*>(a_scales);
-  a.K = is_down ? p.inter : hidden;
+  a.a_stride = a_stride;
+  DMOQ_CHECK_ARG(a_stride >= (is_down ? p.inter : hidden) && a_stride % kG == 0);
   a.out = out;
   a.out_stride = out_stride;
   a.partials = partials;

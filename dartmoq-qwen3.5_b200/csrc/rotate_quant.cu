@@ -22,7 +22,8 @@ constexpr int kXPitch = kRows + 4;
 struct RotArgs {
   const void* x;
   int src_is_bf16;
-  int K;                        // columns of x / of the outputs
+  int K;                        // columns rotated (multiple of 128)
+  int x_stride, o_stride;       // row pitch (elements) of x and of the code table
   const uint16_t* rot;          // fp16 (n_mats, 128, 128)
   const int32_t* src_row;       // optional gather
   int n_rows;
@@ -69,7 +70,7 @@ __device__ void rotq_block(const RotArgs& a, const float* s_p, float* s_x, int g
     const bool valid = r < rows;
     size_t src = 0;
     if (valid) src = a.src_row ? (size_t)a.src_row[row0 + r] : (size_t)(row0 + r);
-    const size_t base = src * (size_t)a.K + (size_t)g * kG + kh * 64;
+    const size_t base = src * (size_t)a.x_stride + (size_t)g * kG + kh * 64;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       float v[8];
@@ -116,7 +117,7 @@ __device__ void rotq_block(const RotArgs& a, const float* s_p, float* s_x, int g
   }
   __syncthreads();  // s_x may be overwritten by the next block
 
-  const int G = a.K / kG;
+  const int G = a.o_stride / kG;
 #pragma unroll
   for (int r = 0; r < 8; ++r) {
     const int lr = ty * 8 + r;
@@ -131,7 +132,7 @@ __device__ void rotq_block(const RotArgs& a, const float* s_p, float* s_x, int g
         __align__(16) __half h[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) h[c] = __float2half_rn(acc[r][c]);
-        *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.codes) + (size_t)orow * a.K + g * kG + tx * 8) =
+        *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.codes) + (size_t)orow * a.o_stride + g * kG + tx * 8) =
             *reinterpret_cast<const uint4*>(h);
       }
     } else if (MODE == DMOQ_A8 || MODE == DMOQ_FP8) {
@@ -151,7 +152,7 @@ __device__ void rotq_block(const RotArgs& a, const float* s_p, float* s_x, int g
         }
       }
       if (valid) {
-        *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(a.codes) + (size_t)orow * a.K + g * kG + tx * 8) =
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(a.codes) + (size_t)orow * a.o_stride + g * kG + tx * 8) =
             *reinterpret_cast<const uint2*>(q);
         if (tx == 0)
           reinterpret_cast<__half*>(a.scales)[(size_t)orow * G + g] = __float2half_rn(__fmul_rn(s, a.extra_scale));
@@ -171,9 +172,9 @@ __device__ void rotq_block(const RotArgs& a, const float* s_p, float* s_x, int g
         word |= (uint32_t)e2m1_nibble(y) << (4 * c);
       }
       if (valid) {
-        *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.codes) + (size_t)orow * (a.K / 2) + (g * kG + tx * 8) / 2) = word;
+        *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.codes) + (size_t)orow * (a.o_stride / 2) + (g * kG + tx * 8) / 2) = word;
         if ((tx & 3) == 0)
-          reinterpret_cast<uint8_t*>(a.scales)[(size_t)orow * (a.K / 32) + g * 4 + tx / 4] = (uint8_t)(int)(e + 127.f);
+          reinterpret_cast<uint8_t*>(a.scales)[(size_t)orow * (a.o_stride / 32) + g * 4 + tx / 4] = (uint8_t)(int)(e + 127.f);
       }
     }
   }
@@ -279,6 +280,8 @@ extern "C" int dmoq_rotate_quant(int32_t mode, const void* x, int32_t src_is_bf1
   a.x = x;
   a.src_is_bf16 = src_is_bf16;
   a.K = K;
+  a.x_stride = K;
+  a.o_stride = K;
   a.rot = rot;
   a.src_row = src_row;
   a.n_rows = n_rows;
@@ -297,7 +300,8 @@ extern "C" int dmoq_rotate_quant(int32_t mode, const void* x, int32_t src_is_bf1
 }
 
 extern "C" int dmoq_rotate_quant_down(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t pool_index,
-                                      const uint16_t* act, void* codes, void* scales, void* stream) {
+                                      const uint16_t* act, int32_t act_stride, void* codes, void* scales,
+                                      int32_t code_stride, void* stream) {
   DMOQ_CHECK_ARG(route && pools_host && act && codes);
   DMOQ_CHECK_ARG(pool_index >= 0 && pool_index < route->n_pools);
   const dmoq_pool_t& p = pools_host[pool_index];
@@ -306,7 +310,10 @@ extern "C" int dmoq_rotate_quant_down(const dmoq_route_t* route, const dmoq_pool
   RotArgs a{};
   a.x = act;
   a.src_is_bf16 = 0;
+  DMOQ_CHECK_ARG(act_stride >= p.inter && act_stride % 8 == 0 && code_stride >= p.inter && code_stride % kG == 0);
   a.K = p.inter;
+  a.x_stride = act_stride;
+  a.o_stride = code_stride;
   a.rot = p.dn_rot;
   a.extra_scale = p.dn_act_scale;
   a.codes = codes;

@@ -74,14 +74,12 @@ __device__ void scan_and_tiles(const RouteArgs& a, int32_t* s_count /* E_tot+1 i
       }
     }
     a.r.expert_rows[E_tot] = run;
-    int src = 0, tb = 0;
+    int tb = 0;
     for (int p = 0; p < DMOQ_MAX_POOLS; ++p) {
       s_tile_base[p] = tb;
       a.r.pool_rows[p] = pool_rows[p];
-      a.r.pool_src_base[p] = src;
       a.r.n_tiles[p] = pool_tiles[p];
       a.r.n_tiles[DMOQ_MAX_POOLS + p] = tb;
-      if (p < P && !a.r.pool_hoisted[p]) src += pool_rows[p];
       tb += pool_tiles[p];
     }
   }

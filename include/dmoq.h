@@ -44,7 +44,7 @@ enum { DMOQ_A16 = 0, DMOQ_A8 = 1, DMOQ_FP8 = 2, DMOQ_FP4 = 3 };
 enum {
   DMOQ_EPI_SILU = 0,     /* tile = [gate | up]; store silu(gate)*up as fp16 (I columns)   */
   DMOQ_EPI_WEIGHTED = 1, /* store bf16(bf16(fp16(acc)) * row_weight)  (down projection)   */
-  DMOQ_EPI_PLAIN = 2     /* store fp16(acc)                                                */
+  DMOQ_EPI_PLAIN = 2     /* store fp16(acc); gate_up form: (R, 2*inter) = [gate | up]      */
 };
 
 #define DMOQ_GROUP 128      /* quantisation group = rotation block, fixed by the format */
@@ -101,11 +101,12 @@ typedef struct dmoq_route {
   int32_t* row_of;            /* (R) row of flat (token, slot) pair; shared rows follow        */
   int32_t* a_row;             /* (R) row of the pool's activation-code table feeding this row  */
   int32_t* pool_rows;         /* (DMOQ_MAX_POOLS) rows routed to each pool                     */
-  int32_t* pool_src;          /* (R) for non-hoisted pools: token of each compact table row,
-                                 pool p's list starts at pool_src_base[p]                      */
-  int32_t* pool_src_base;     /* (DMOQ_MAX_POOLS) */
+  int32_t* pool_src;          /* for non-hoisted pools: token of each compact table row,
+                                 pool p's list starts at pool_src_base[p]; size = sum of the
+                                 non-hoisted pools' act_cap_rows                               */
+  const int32_t* pool_src_base; /* (DMOQ_MAX_POOLS) static: first pool_src entry of each non-hoisted pool */
   int32_t* tiles;             /* (tile_cap, 4): expert, first row, row count, pool             */
-  int32_t* n_tiles;           /* (DMOQ_MAX_POOLS+1) tiles per pool, then exclusive prefix base  */
+  int32_t* n_tiles;           /* (2*DMOQ_MAX_POOLS) tiles per pool, then each pool's first tile  */
   int32_t tile_cap;
   const int32_t* pool_hoisted;/* (DMOQ_MAX_POOLS) static copy of dmoq_pool_t.hoisted           */
 } dmoq_route_t;
@@ -153,10 +154,12 @@ int dmoq_rotate_quant(int32_t mode, const void* x, int32_t src_is_bf16, int32_t 
  * (quantization/wxa8/bit_partitioned_moe.py:346-358): rows are taken from the
  * tile lists of `route`, the rotation of row r / group g is
  * pool.dn_rot[rank(expert(r))*inter/128 + g].
- *   act (R, inter) fp16 -> codes/scales laid out as in dmoq_rotate_quant with K = inter
+ *   act (R, act_stride) fp16 -> codes/scales laid out as in dmoq_rotate_quant, rows pitched by
+ *   code_stride elements (scales by code_stride/128 resp. code_stride/32)
  */
 int dmoq_rotate_quant_down(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t pool_index,
-                           const uint16_t* act, void* codes, void* scales, void* stream);
+                           const uint16_t* act, int32_t act_stride, void* codes, void* scales,
+                           int32_t code_stride, void* stream);
 
 /*
  * Grouped LUT-dequant GEMM over one pool's tile list.
@@ -168,13 +171,13 @@ int dmoq_rotate_quant_down(const dmoq_route_t* route, const dmoq_pool_t* pools_h
  *            replaces *_matmul_merged_in_features_gf + dn.mul_(w)
  *            (triton_kernels.py:1554, triton_kernels_a8.py:1017, triton_kernels_fp8.py:699,
  *             triton_kernels_fp4.py:811; quantization/wxa16/bit_partitioned_moe.py:960-966)
- * `a_codes`/`a_scales` are the pool's activation table; rows are gathered through
+ * `a_codes`/`a_scales` are the pool's activation table (row pitch a_stride elements); rows are gathered through
  * route->a_row (gate_up) or taken at the row's own index (down).
  * `partials` (optional, A8 only): int32 (R, N, G) per-group integer sums for parity checks.
  */
 int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t pool_index,
                       int32_t is_down, int32_t epilogue, int32_t hidden,
-                      const void* a_codes, const void* a_scales,
+                      const void* a_codes, const void* a_scales, int32_t a_stride,
                       void* out, int32_t out_stride, int32_t* partials, void* stream);
 
 /*
