@@ -292,6 +292,7 @@ class _Engine:
         self.pool_hoisted = torch.tensor([int(p.hoisted) for p in self.pools] + [0] * (MAX_POOLS - len(self.pools)), **i32)
         self.pool_array = (Pool * len(self.pools))()
         self._ws: Dict[int, _Workspace] = {}
+        self.last_launches = 0
 
     # ------------------------------------------------------------------ per-T buffers
     def workspace(self, T: int) -> _Workspace:
@@ -377,6 +378,8 @@ class _Engine:
         check(lib.dmoq_route_build(C.byref(ws.route), ptr(topk_idx), ptr(topk_w), ptr(shared_w),
                                    ptr(ws.route_ws), ws.route_ws.numel(), s), "dmoq_route_build")
         mark("route")
+        # kernels launched by this forward: routing is one fused launch for <= 1024 routed pairs, else three
+        self.last_launches = (1 if T * self.k_v <= 1024 and T <= 4096 else 3) + 4 * len(self.pools) + 1
         for i, p in enumerate(self.pools):
             p.c.act_cap_rows = ws.caps[i]
             p.c.act_codes, p.c.act_scales = ws.act_codes[i].data_ptr(), ws.act_scales[i].data_ptr()
@@ -392,7 +395,7 @@ class _Engine:
             check(lib.dmoq_grouped_gemm(C.byref(ws.route), self.pool_array, i, 0, EPI_SILU, self.hidden,
                                         ptr(ws.act_codes[i]), ptr(ws.act_scales[i]), self.hidden,
                                         ptr(ws.act), self.inter_max, ptr(part), s), "dmoq_grouped_gemm(gate_up)")
-        mark("gate_up_silu")
+            mark("gate_up_silu:" + p.key)
         for i, p in enumerate(self.pools):
             check(lib.dmoq_rotate_quant_down(C.byref(ws.route), self.pool_array, i, ptr(ws.act), self.inter_max,
                                              ptr(ws.dn_codes), ptr(ws.dn_scales), self.inter_max, s),
@@ -403,7 +406,7 @@ class _Engine:
             check(lib.dmoq_grouped_gemm(C.byref(ws.route), self.pool_array, i, 1, EPI_WEIGHTED, self.hidden,
                                         ptr(ws.dn_codes), ptr(ws.dn_scales), self.inter_max,
                                         ptr(ws.dn), self.hidden, ptr(part), s), "dmoq_grouped_gemm(down)")
-        mark("down_weighted")
+            mark("down_weighted:" + p.key)
         y = torch.empty_like(x)
         check(lib.dmoq_combine(C.byref(ws.route), ptr(ws.dn), self.hidden, ptr(y), is_bf16, s), "dmoq_combine")
         mark("combine")

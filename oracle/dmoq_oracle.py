@@ -103,7 +103,7 @@ def rotation(d: int, seed: int) -> np.ndarray:
         gen = torch.Generator().manual_seed(seed)
         q, r = torch.linalg.qr(torch.randn(d, d, generator=gen))
         _ROT[key] = (q * torch.sign(torch.diag(r)).unsqueeze(0)).numpy().copy()
-        if len(_ROT) > 8192:
+        if len(_ROT) > 16384:
             _ROT.pop(next(iter(_ROT)))
     return _ROT[key]
 
@@ -133,17 +133,26 @@ def quantize_packed(W: np.ndarray, bit: int, seed: int, uniform: bool = False) -
 
 
 def dequantize_packed(pk: dict) -> np.ndarray:
-    """turboquant_utils/quantize.py:478-557: fp32 matrix (before the cast to the original dtype)."""
+    """turboquant_utils/quantize.py:478-557: fp32 matrix (before the cast to the original dtype).
+
+    Uses the same torch CPU operations as the reference (unpack by shifts, codebook gather, one
+    (N,128)x(128,128) matmul per group), so its run time is representative of the reference's.
+    """
     n, k = pk["shape"]
-    cb = np.asarray(pk["codebook"], np.float32)
-    norms = np.asarray(pk["norms"], np.float32).reshape(n, -1)
-    idx = unpack_nbit(np.asarray(pk["indices_packed"]), pk["bit_width"], k)
-    out = np.zeros((n, k), np.float32)
+    bit = pk["bit_width"]
+    per = 8 // bit
+    cb = torch.from_numpy(np.asarray(pk["codebook"], np.float32))
+    norms = torch.from_numpy(np.asarray(pk["norms"], np.float32).reshape(n, -1))
+    packed = torch.from_numpy(np.ascontiguousarray(pk["indices_packed"]))
+    idx = torch.zeros(n, packed.shape[1] * per, dtype=torch.int32)
+    for j in range(per):
+        idx[:, j::per] = ((packed >> (j * bit)) & ((1 << bit) - 1)).to(torch.int32)
+    idx = idx[:, :k]
+    out = torch.zeros(n, k, dtype=torch.float32)
     for g, g0 in enumerate(range(0, k, GS)):
-        y = torch.from_numpy(cb[idx[:, g0:g0 + GS]]) / math.sqrt(GS)
-        w = (y @ torch.from_numpy(rotation(GS, pk["seed"] + g0))).numpy()
-        out[:, g0:g0 + GS] = w * norms[:, g:g + 1]
-    return out
+        y = cb[idx[:, g0:g0 + GS]] / math.sqrt(GS)
+        out[:, g0:g0 + GS] = (y @ torch.from_numpy(rotation(GS, pk["seed"] + g0))) * norms[:, g:g + 1]
+    return out.numpy()
 
 
 # =========================================================================== activation-mode LUTs
@@ -390,6 +399,15 @@ class Layer:
             pk["idx_gf"] = idx_gf
             # norms_gf / sqrt(128) in fp16 (quantization/wxa16/bit_partitioned_moe.py:203)
             pk["norm_gf"] = (norm_gf.astype(np.float32) / np.float32(math.sqrt(GS))).astype(np.float16)
+
+
+def warm_rotations(layer: "Layer") -> None:
+    """Fill the rotation cache for every group of every pool (the reference caches them too, rotation.py:33-41)."""
+    for p in layer.pools + ([layer.shared] if layer.shared else []):
+        for side in ("gu", "dn"):
+            k = p[side]["shape"][1]
+            for g0 in range(0, k, GS):
+                rotation(GS, p[side]["seed"] + g0)
 
 
 def sort_rows(topk_idx: np.ndarray, topk_w: np.ndarray, n_experts: int):
