@@ -396,12 +396,13 @@ class _Engine:
                                         ptr(ws.act_codes[i]), ptr(ws.act_scales[i]), self.hidden,
                                         ptr(ws.act), self.inter_max, ptr(part), s), "dmoq_grouped_gemm(gate_up)")
             mark("gate_up_silu:" + p.key)
+        # down side, pool by pool: the code / scale scratch is shared by all pools and its byte pitch
+        # depends on the pool's mode, so a pool's codes are consumed before the next pool writes its own
         for i, p in enumerate(self.pools):
             check(lib.dmoq_rotate_quant_down(C.byref(ws.route), self.pool_array, i, ptr(ws.act), self.inter_max,
                                              ptr(ws.dn_codes), ptr(ws.dn_scales), self.inter_max, s),
                   "dmoq_rotate_quant_down")
-        mark("rotate_quant_down")
-        for i, p in enumerate(self.pools):
+            mark("rotate_quant_down:" + p.key)
             part = None if partials is None else partials.get(("down", p.key))
             check(lib.dmoq_grouped_gemm(C.byref(ws.route), self.pool_array, i, 1, EPI_WEIGHTED, self.hidden,
                                         ptr(ws.dn_codes), ptr(ws.dn_scales), self.inter_max,

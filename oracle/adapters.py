@@ -49,8 +49,8 @@ def routing(moe, x):
         w, idx = out.softmax(dim=-1).topk(moe.top_k, dim=-1)
     sw = None
     if moe.shared_expert is not None and moe.shared_expert_gate is not None:
-        sw = torch.sigmoid(moe.shared_expert_gate(x)).reshape(-1).float().cpu().numpy()
-    return w.float().cpu().numpy(), idx.cpu().numpy(), sw
+        sw = torch.sigmoid(moe.shared_expert_gate(x)).detach().reshape(-1).float().cpu().numpy()
+    return w.detach().float().cpu().numpy(), idx.cpu().numpy(), sw
 
 
 def rel_fro(a, b) -> float:
