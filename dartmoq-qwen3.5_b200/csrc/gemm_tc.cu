@@ -1,0 +1,598 @@
+// Grouped LUT-dequant GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), INT8 and e4m3 modes.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warps 0-7   epilogue: drain the per-group accumulator from TMEM (tcgen05.ld), fold
+//               (acc * row_scale) * col_norm into an fp32 running total, final SiLU*up or
+//               routing-weight epilogue through a padded shared-memory staging tile
+//   warps 8-11  producers: gather activation-code rows with cp.async straight into the 128B-swizzled
+//               K-major operand tile; copy the packed codebook indices with cp.async into a raw ring
+//               and expand them in registers (byte-permute lookups) into the swizzled B operand tile
+//   warp 12     one elected thread issues tcgen05.mma (M=128, N=128, K=32 x4 per 128-wide group),
+//               tcgen05.commit releases the smem stage and publishes the accumulator
+// Accumulators are double-buffered in TMEM (2 x 128 columns), so the tensor pipe works on group g+1
+// while the epilogue warps scale group g.  Integer group sums are exact (kind::i8, int32), which is
+// what turboquant_utils/triton_kernels_a8.py:893-929 computes; kind::f8f6f4 gives the fp32 group sums of
+// turboquant_utils/triton_kernels_fp8.py:589-626.
+//
+// Every wait on an mbarrier is bounded; on a timeout the CTA raises a flag in the device status word,
+// stops issuing work, and falls through to the common teardown (TMEM is always released).
+#include "common.cuh"
+
+namespace {
+
+constexpr int kBM = 128, kBN = 128, kG = DMOQ_GROUP;
+constexpr int kStages = 4;       // operand ring depth (one 128-wide group per stage)
+constexpr int kLag = 2;          // producer: stages between issuing the async copies and expanding them
+constexpr int kEpiWarps = 8, kProdWarps = 4;
+constexpr int kThreads = 32 * (kEpiWarps + kProdWarps + 1);
+constexpr int kGMax = 24;        // groups along K per member supported by the scale tiles (K <= 3072)
+constexpr int kTileB = kBM * kG; // bytes of one int8 / e4m3 operand tile
+constexpr int kOutPitch = 272;   // bytes per staged output row (256 + 16: conflict-free 16-byte stores)
+constexpr uint32_t kSpinLimit = 1u << 26;
+constexpr long long kWaitCycles = 2000000000LL;
+
+__device__ int g_dmoq_tc_status = 0;
+
+struct TcArgs {
+  const DmoqTile* tiles;
+  const int32_t* n_tiles;
+  const int32_t* expert_rank;
+  const int32_t* a_row;
+  const float* row_weight;
+  int pool, is_down, inter, hidden, n_members;
+  const uint8_t* idx;
+  const uint16_t* norm;
+  const uint8_t* lut;
+  int identity_lut;
+  const uint8_t* a_codes;
+  const uint16_t* a_scales;
+  int a_stride;
+  void* out;
+  int out_stride;
+  int32_t* partials;
+};
+
+// ------------------------------------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait (about one second of SM clock).  Returns false, and raises the abort flag, if the phase
+// never completes; once the flag is up every later wait returns at once.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (*abort_flag) return false;
+  const long long t0 = clock64();
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 63u) == 63u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycles) break;
+    }
+  }
+  *abort_flag = 1;
+  atomicOr(&g_dmoq_tc_status, 1);
+  return false;
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void bar_sync_epi() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory"); }
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+__device__ __forceinline__ void cp_async_n(void* smem, const void* gmem, int bytes) {
+  if (bytes == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem));
+  else if (bytes == 8) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem)), "l"(gmem));
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem)), "l"(gmem));
+}
+
+// K-major, 128-byte swizzle: tile row r is 128 bytes; 16-byte chunk c lives at slot c ^ (r & 7);
+// groups of 8 rows are 1024 bytes apart (the descriptor's stride byte offset).
+__device__ __forceinline__ uint32_t swz128(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+// Codeword tables for the in-register expansion: up to 16 one-byte codewords in four registers.
+struct Lut {
+  uint32_t w[4];
+};
+
+// 16 consecutive weights (one 16-byte chunk of the operand row) from their packed indices.
+template <int BIT>
+__device__ __forceinline__ uint4 expand16(const uint32_t* raw, const Lut& lut, bool identity) {
+  uint32_t o[4];
+  if (BIT == 8) {  // raw[0..3] = 16 index bytes
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (identity) {
+        o[q] = raw[q] ^ 0x80808080u;  // index - 128 as int8
+      } else {
+        o[q] = 0;  // general 256-entry tables take the warp-level MMA path
+      }
+    }
+  } else if (BIT == 4) {  // raw[0..1] = 16 nibbles
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t w = raw[h];
+      const uint32_t sel = w & 0x77777777u, hi = (w >> 1) & 0x44444444u;
+      const uint32_t lo_a = prmt(lut.w[0], lut.w[1], sel), hi_a = prmt(lut.w[2], lut.w[3], sel);
+      const uint32_t lo_b = prmt(lut.w[0], lut.w[1], sel >> 16), hi_b = prmt(lut.w[2], lut.w[3], sel >> 16);
+      o[2 * h + 0] = prmt(lo_a, hi_a, (hi & 0xFFFFu) | 0x3210u);
+      o[2 * h + 1] = prmt(lo_b, hi_b, (hi >> 16) | 0x3210u);
+    }
+  } else if (BIT == 2) {  // raw[0] = 16 two-bit fields
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t s = (raw[0] >> (16 * h)) & 0xFFFFu;
+      s = (s | (s << 8)) & 0x00FF00FFu;
+      s = (s | (s << 4)) & 0x0F0F0F0Fu;
+      s = (s | (s << 2)) & 0x33333333u;
+      o[2 * h + 0] = prmt(lut.w[0], lut.w[0], s);
+      o[2 * h + 1] = prmt(lut.w[0], lut.w[0], s >> 16);
+    }
+  } else {  // BIT == 1: low 16 bits of raw[0]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t s = (raw[0] >> (8 * h)) & 0xFFu;
+      s = (s | (s << 12)) & 0x000F000Fu;
+      s = (s | (s << 6)) & 0x03030303u;
+      s = (s | (s << 3)) & 0x11111111u;
+      o[2 * h + 0] = prmt(lut.w[0], lut.w[0], s);
+      o[2 * h + 1] = prmt(lut.w[0], lut.w[0], s >> 16);
+    }
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+struct Smem {
+  // operand ring, 1024-byte aligned tiles
+  uint8_t a[kStages][kTileB];
+  uint8_t b[kStages][kTileB];
+  uint8_t raw[kStages][kBN * 64];   // packed indices of one group (<= 64 bytes per row: 4-bit)
+  uint8_t out[kBM * kOutPitch];
+  float norm[kGMax * kBN];
+  float xs[kGMax * kBM];
+  uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int MODE, int BIT, int EPI>
+__global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  volatile int* abort_flag = &S.abort_flag;
+  constexpr int BPG = 16 * BIT;                       // packed bytes per row per group
+  constexpr int RAWB = (BIT == 1) ? 4 : BPG / 8;      // bytes one cp.async moves (1-bit: two chunks at once)
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&S.full[s], kProdWarps);
+      mbar_init(&S.empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&S.acc_full[b], 1);
+      mbar_init(&S.acc_empty[b], kEpiWarps);
+    }
+    S.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kEpiWarps + kProdWarps) {  // the MMA warp owns the TMEM allocation
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&S.tmem_base)),
+                 "r"(2 * kBN));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = S.tmem_base;
+
+  const int n_tiles = a.n_tiles[a.pool];
+  const DmoqTile* tiles = a.tiles + a.n_tiles[DMOQ_MAX_POOLS + a.pool];
+  const int NB = a.is_down ? a.hidden / kBN : a.inter / (kBN / 2);
+  const int G = a.is_down ? a.inter / kG : a.hidden / kG;
+  const int n_total = a.is_down ? a.hidden : a.n_members * 2 * a.inter;
+  const int n_work = n_tiles * NB;
+
+  if (warp < kEpiWarps) {
+    // =========================================================================== epilogue warps
+    const int quarter = warp & 3, half = warp >> 2;
+    const int r = quarter * 32 + lane;               // tile row == TMEM lane
+    const int etid = warp * 32 + lane;
+    uint32_t ia = 0;                                  // accumulator uses so far
+    for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
+      const DmoqTile tile = tiles[w / NB];
+      const int nb = w % NB;
+      const int rank = a.expert_rank[tile.expert];
+      const int gg0 = a.is_down ? rank * G : 0;
+      const int seg0 = a.is_down ? nb * kBN : rank * 2 * a.inter + nb * (kBN / 2);
+      const int seg1 = a.is_down ? seg0 : seg0 + a.inter;
+      const bool row_ok = r < tile.rows;
+      const int grow = tile.row0 + r;
+      const int arow = row_ok ? (a.a_row ? a.a_row[grow] : grow) : -1;
+
+      bar_sync_epi();  // the previous item's readers of norm / out are done
+      for (int i = etid; i < G * kBN; i += 32 * kEpiWarps) {
+        const int g = i / kBN, c = i % kBN;
+        const int n = a.is_down ? seg0 + c : ((c & 1) ? seg1 : seg0) + (c >> 1);
+        S.norm[i] = __half2float(reinterpret_cast<const __half*>(a.norm)[(size_t)(gg0 + g) * n_total + n]);
+      }
+      if (half == 0) {
+        for (int g = 0; g < G; ++g)
+          S.xs[g * kBM + r] =
+              row_ok ? __half2float(reinterpret_cast<const __half*>(a.a_scales)[(size_t)arow * (a.a_stride / kG) + g]) : 0.f;
+      }
+      bar_sync_epi();
+
+      float total[64];
+#pragma unroll
+      for (int c = 0; c < 64; ++c) total[c] = 0.f;
+
+      for (int g = 0; g < G; ++g, ++ia) {
+        const uint32_t b = ia & 1, ph = (ia >> 1) & 1;
+        mbar_wait(&S.acc_full[b], ph, abort_flag);  // on a timeout the flag is raised and the data is void
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + b * kBN + half * 64;
+        const float xs = S.xs[g * kBM + r];
+        const float* nrm = &S.norm[g * kBN + half * 64];
+        const int n_out = a.is_down ? a.hidden : 2 * a.inter;
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {   // two 32-column loads keep the register footprint down
+          uint32_t v[32];
+          tc_ld32(taddr + part * 32, v);
+          tc_wait_ld();
+          if (part == 1) {                         // the accumulator buffer can be overwritten now
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&S.acc_empty[b]);
+          }
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const float f = (MODE == DMOQ_A8) ? (float)(int32_t)v[c] : __uint_as_float(v[c]);
+            total[part * 32 + c] = __fadd_rn(total[part * 32 + c], __fmul_rn(__fmul_rn(f, xs), nrm[part * 32 + c]));
+          }
+          if (MODE == DMOQ_A8 && a.partials != nullptr && row_ok) {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const int col = half * 64 + part * 32 + c;
+              const int n = a.is_down ? nb * kBN + col : (col & 1) * a.inter + nb * (kBN / 2) + (col >> 1);
+              a.partials[((size_t)grow * n_out + n) * G + g] = (int32_t)v[c];
+            }
+          }
+        }
+      }
+      // ---- tile epilogue through the staging tile
+      if (EPI == DMOQ_EPI_SILU) {
+        __align__(16) __half o[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float gate = __half2float(__float2half_rn(total[2 * i]));
+          const float up = __half2float(__float2half_rn(total[2 * i + 1]));
+          const float sg = __half2float(__float2half_rn(__fdiv_rn(gate, 1.0f + expf(-gate))));
+          o[i] = __float2half_rn(__fmul_rn(sg, up));
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(&S.out[r * kOutPitch + half * 64 + q * 16]) = reinterpret_cast<const uint4*>(o)[q];
+        bar_sync_epi();
+        __half* out = reinterpret_cast<__half*>(a.out);
+        for (int i = etid; i < kBM * 8; i += 32 * kEpiWarps) {
+          const int rr = i >> 3, ch = i & 7;
+          if (rr < tile.rows)
+            *reinterpret_cast<uint4*>(out + (size_t)(tile.row0 + rr) * a.out_stride + nb * 64 + ch * 8) =
+                *reinterpret_cast<const uint4*>(&S.out[rr * kOutPitch + ch * 16]);
+        }
+      } else if (EPI == DMOQ_EPI_PLAIN && !a.is_down) {
+        __half* out = reinterpret_cast<__half*>(a.out);
+        if (row_ok) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) {
+            const int col = half * 64 + c;
+            const int n = (col & 1) * a.inter + nb * (kBN / 2) + (col >> 1);
+            out[(size_t)grow * a.out_stride + n] = __float2half_rn(total[c]);
+          }
+        }
+      } else {
+        const float wgt = (EPI == DMOQ_EPI_WEIGHTED && row_ok) ? a.row_weight[grow] : 0.f;
+        __align__(16) uint16_t o[64];
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const __half h16 = __float2half_rn(total[c]);
+          if (EPI == DMOQ_EPI_WEIGHTED) {
+            const __nv_bfloat16 bb = __float2bfloat16_rn(__half2float(h16));
+            o[c] = __bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(__bfloat162float(bb), wgt)));
+          } else {
+            o[c] = __half_as_ushort(h16);
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<uint4*>(&S.out[r * kOutPitch + half * 128 + q * 16]) = reinterpret_cast<const uint4*>(o)[q];
+        bar_sync_epi();
+        uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
+        for (int i = etid; i < kBM * 16; i += 32 * kEpiWarps) {
+          const int rr = i >> 4, ch = i & 15;
+          if (rr < tile.rows)
+            *reinterpret_cast<uint4*>(out + (size_t)(tile.row0 + rr) * a.out_stride + nb * kBN + ch * 8) =
+                *reinterpret_cast<const uint4*>(&S.out[rr * kOutPitch + ch * 16]);
+        }
+      }
+    }
+  } else if (warp < kEpiWarps + kProdWarps) {
+    // =========================================================================== producer warps
+    const int pt = tid - 32 * kEpiWarps;              // 0..127
+    Lut lut;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) lut.w[q] = 0;
+    if (!(BIT == 8)) {
+      for (int i = 0; i < (1 << BIT); ++i) lut.w[i >> 2] |= (uint32_t)a.lut[i] << (8 * (i & 3));
+    }
+    // chunk ownership: 8 (row, 16-byte chunk) pairs per thread and stage, chosen so that a warp's
+    // stores fall on distinct shared-memory bank groups
+    auto own_row = [&](int i) { return (BIT == 1) ? (pt >> 2) + 32 * (i >> 1) : (pt >> 3) + 16 * i; };
+    auto own_chunk = [&](int i) { return (BIT == 1) ? 2 * (pt & 3) + (i & 1) : (pt & 7); };
+
+    uint32_t it = 0;       // stages issued
+    uint32_t done = 0;     // stages expanded and published
+    auto publish = [&](uint32_t j) {
+      const int s = j % kStages;
+      if (BIT != 8) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int row = own_row(i), ch = own_chunk(i);
+          uint32_t raw[2];
+          if (BIT == 4) {
+            const uint2 v = *reinterpret_cast<const uint2*>(&S.raw[s][row * BPG + ch * 8]);
+            raw[0] = v.x;
+            raw[1] = v.y;
+          } else if (BIT == 2) {
+            raw[0] = *reinterpret_cast<const uint32_t*>(&S.raw[s][row * BPG + ch * 4]);
+          } else {
+            const uint32_t v = *reinterpret_cast<const uint32_t*>(&S.raw[s][row * BPG + (ch >> 1) * 4]);
+            raw[0] = (ch & 1) ? (v >> 16) : (v & 0xFFFFu);
+          }
+          *reinterpret_cast<uint4*>(&S.b[s][swz128(row, ch)]) = expand16<BIT>(raw, lut, false);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          uint4* p = reinterpret_cast<uint4*>(&S.b[s][swz128(own_row(i), own_chunk(i))]);
+          uint4 v = *p;
+          uint32_t raw[4] = {v.x, v.y, v.z, v.w};
+          *p = expand16<8>(raw, lut, true);
+        }
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&S.full[s]);
+    };
+
+    for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
+      const DmoqTile tile = tiles[w / NB];
+      const int nb = w % NB;
+      const int rank = a.expert_rank[tile.expert];
+      const int gg0 = a.is_down ? rank * G : 0;
+      const int seg0 = a.is_down ? nb * kBN : rank * 2 * a.inter + nb * (kBN / 2);
+      const int seg1 = a.is_down ? seg0 : seg0 + a.inter;
+      // activation rows this thread copies: row (pt>>3) + 16*i, chunk pt&7
+      int arow[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = (pt >> 3) + 16 * i;
+        const int grow = tile.row0 + rr;
+        arow[i] = rr < tile.rows ? (a.a_row ? a.a_row[grow] : grow) : -1;
+      }
+      for (int g = 0; g < G; ++g, ++it) {
+        const int s = it % kStages;
+        mbar_wait(&S.empty[s], ((it / kStages) & 1) ^ 1, abort_flag);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int rr = (pt >> 3) + 16 * i, ch = pt & 7;
+          const uint8_t* src = a.a_codes + (size_t)(arow[i] < 0 ? 0 : arow[i]) * a.a_stride + (size_t)g * kG + ch * 16;
+          cp_async16_zfill(&S.a[s][swz128(rr, ch)], src, arow[i] >= 0);
+        }
+        if (BIT == 1) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {  // one 4-byte copy covers two adjacent chunks
+            const int row = (pt >> 2) + 32 * i, pair = pt & 3;
+            const int n = a.is_down ? seg0 + row : ((row & 1) ? seg1 : seg0) + (row >> 1);
+            cp_async_n(&S.raw[s][row * BPG + pair * 4], a.idx + ((size_t)(gg0 + g) * n_total + n) * BPG + pair * 4, 4);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int row = own_row(i), ch = own_chunk(i);
+            const int n = a.is_down ? seg0 + row : ((row & 1) ? seg1 : seg0) + (row >> 1);
+            const uint8_t* src = a.idx + ((size_t)(gg0 + g) * n_total + n) * BPG + ch * RAWB;
+            if (BIT == 8) cp_async_n(&S.b[s][swz128(row, ch)], src, 16);
+            else cp_async_n(&S.raw[s][row * BPG + ch * RAWB], src, RAWB);
+          }
+        }
+        cp_async_commit();
+        if (it - done >= (uint32_t)kLag) {
+          cp_async_wait<kLag>();
+          publish(done++);
+        }
+      }
+    }
+    // drain: everything issued must be published so the MMA warp and the epilogue can finish
+    while (done < it) {
+      const uint32_t pending = it - done - 1;
+      if (pending >= 1) cp_async_wait<1>(); else cp_async_wait<0>();
+      publish(done++);
+    }
+  } else {
+    // =========================================================================== MMA warp
+    constexpr uint32_t idesc_i8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+    constexpr uint32_t idesc_f8 = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+    uint32_t it = 0;
+    for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
+      for (int g = 0; g < G; ++g, ++it) {
+        const int s = it % kStages;
+        const uint32_t b = it & 1;
+        bool ok = mbar_wait(&S.full[s], (it / kStages) & 1, abort_flag);
+        ok = ok && mbar_wait(&S.acc_empty[b], ((it >> 1) & 1) ^ 1, abort_flag);
+        tc_fence_after();
+        if (lane == 0 && ok) {
+          const uint64_t da = make_desc(smem_u32(&S.a[s][0]));
+          const uint64_t db = make_desc(smem_u32(&S.b[s][0]));
+          const uint32_t d = tmem_base + b * kBN;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {  // K = 32 bytes per instruction: +2 in 16-byte units
+            if (MODE == DMOQ_A8) tc_mma_i8(d, da + 2 * k, db + 2 * k, idesc_i8, k > 0);
+            else tc_mma_f8(d, da + 2 * k, db + 2 * k, idesc_f8, k > 0);
+          }
+          tc_commit(&S.empty[s]);
+          tc_commit(&S.acc_full[b]);
+        }
+        __syncwarp();
+      }
+    }
+  }
+
+  // ---- teardown: all roles meet here, then the allocating warp releases TMEM
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kEpiWarps + kProdWarps) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * kBN));
+  }
+}
+
+template <int MODE, int BIT, int EPI>
+int launch(const TcArgs& a, int work_cap, cudaStream_t s) {
+  static bool configured = false;
+  const int bytes = (int)sizeof(Smem) + 1024;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<MODE, BIT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+      return DMOQ_ELAUNCH;
+    configured = true;
+  }
+  int grid = dmoq_sm_count();
+  if (grid > work_cap) grid = work_cap;
+  if (grid < 1) grid = 1;
+  gemm_tc_kernel<MODE, BIT, EPI><<<grid, kThreads, bytes, s>>>(a);
+  return dmoq_launch_status();
+}
+
+template <int MODE, int BIT>
+int launch_epi(const TcArgs& a, int epi, int work_cap, cudaStream_t s) {
+  switch (epi) {
+    case DMOQ_EPI_SILU: return launch<MODE, BIT, DMOQ_EPI_SILU>(a, work_cap, s);
+    case DMOQ_EPI_WEIGHTED: return launch<MODE, BIT, DMOQ_EPI_WEIGHTED>(a, work_cap, s);
+    case DMOQ_EPI_PLAIN: return launch<MODE, BIT, DMOQ_EPI_PLAIN>(a, work_cap, s);
+    default: return DMOQ_EINVAL;
+  }
+}
+
+template <int MODE>
+int launch_bit(const TcArgs& a, int bit, int epi, int work_cap, cudaStream_t s) {
+  switch (bit) {
+    case 1: return launch_epi<MODE, 1>(a, epi, work_cap, s);
+    case 2: return launch_epi<MODE, 2>(a, epi, work_cap, s);
+    case 4: return launch_epi<MODE, 4>(a, epi, work_cap, s);
+    case 8: return launch_epi<MODE, 8>(a, epi, work_cap, s);
+    default: return DMOQ_EINVAL;
+  }
+}
+
+}  // namespace
+
+// True when the tensor-core kernel covers this pool/direction; other cases use the warp-level MMA kernel.
+bool dmoq_tc_supported(const dmoq_pool_t& p, int is_down, int hidden) {
+  if (p.mode != DMOQ_A8 && p.mode != DMOQ_FP8) return false;
+  if (p.bit == 8 && !(p.mode == DMOQ_A8 && p.identity_lut)) return false;
+  const int G = is_down ? p.inter / kG : hidden / kG;
+  return G >= 1 && G <= kGMax;
+}
+
+int dmoq_grouped_gemm_tc(const dmoq_route_t* route, const dmoq_pool_t& p, int pool_index, int is_down, int epilogue,
+                         int hidden, const void* a_codes, const void* a_scales, int a_stride, void* out, int out_stride,
+                         int32_t* partials, cudaStream_t s) {
+  TcArgs a{};
+  a.tiles = reinterpret_cast<const DmoqTile*>(route->tiles);
+  a.n_tiles = route->n_tiles;
+  a.expert_rank = route->expert_rank;
+  a.a_row = is_down ? nullptr : route->a_row;
+  a.row_weight = route->sorted_weights;
+  a.pool = pool_index;
+  a.is_down = is_down;
+  a.inter = p.inter;
+  a.hidden = hidden;
+  a.n_members = p.n_members;
+  a.idx = is_down ? p.dn_idx : p.gu_idx;
+  a.norm = is_down ? p.dn_norm : p.gu_norm;
+  a.lut = static_cast<const uint8_t*>(is_down ? p.dn_lut : p.gu_lut);
+  a.identity_lut = p.identity_lut;
+  a.a_codes = static_cast<const uint8_t*>(a_codes);
+  a.a_scales = static_cast<const uint16_t*>(a_scales);
+  a.a_stride = a_stride;
+  a.out = out;
+  a.out_stride = out_stride;
+  a.partials = partials;
+  const int nb = is_down ? hidden / kBN : p.inter / (kBN / 2);
+  long long cap = (long long)route->tile_cap * nb;
+  const int work_cap = cap > (1 << 30) ? (1 << 30) : (int)cap;
+  if (p.mode == DMOQ_A8) return launch_bit<DMOQ_A8>(a, p.bit, epilogue, work_cap, s);
+  return launch_bit<DMOQ_FP8>(a, p.bit, epilogue, work_cap, s);
+}
+
+// Device status word of the tensor-core kernels: 0 = no bounded wait has ever timed out on this device.
+extern "C" int dmoq_tc_status(int32_t* status_host) {
+  if (!status_host) return DMOQ_EINVAL;
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_dmoq_tc_status, sizeof(int)) != cudaSuccess) return DMOQ_EDEVICE;
+  *status_host = v;
+  return DMOQ_OK;
+}

@@ -13,6 +13,8 @@
 // The gate_up tile interleaves gate and up columns so the SiLU*up epilogue
 // (quantization/wxa16/bit_partitioned_moe.py:925-931) happens in registers; the
 // down tile applies the fp16 -> bf16 -> x routing-weight chain of :960-966.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -445,6 +447,22 @@ int launch_bit(const GemmArgs& a, int bit, int epi, int work_cap, cudaStream_t s
 
 }  // namespace
 
+bool dmoq_tc_supported(const dmoq_pool_t& p, int is_down, int hidden);
+int dmoq_grouped_gemm_tc(const dmoq_route_t* route, const dmoq_pool_t& p, int pool_index, int is_down, int epilogue,
+                         int hidden, const void* a_codes, const void* a_scales, int a_stride, void* out, int out_stride,
+                         int32_t* partials, cudaStream_t s);
+
+// DMOQ_GEMM=mma forces the warp-level MMA kernel for every pool (A/B comparisons); default picks the
+// tcgen05 kernel wherever it applies.
+static bool use_tc_path() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* v = getenv("DMOQ_GEMM");
+    cached = (v && v[0] == 'm') ? 0 : 1;
+  }
+  return cached == 1;
+}
+
 extern "C" int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t pool_index,
                                  int32_t is_down, int32_t epilogue, int32_t hidden,
                                  const void* a_codes, const void* a_scales, int32_t a_stride,
@@ -459,6 +477,12 @@ extern "C" int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* p
   DMOQ_CHECK_ARG(!(epilogue == DMOQ_EPI_SILU && is_down) && !(epilogue == DMOQ_EPI_WEIGHTED && !is_down));
   DMOQ_CHECK_ARG(out_stride % 8 == 0);
   if (p.bit == 8 && p.mode == DMOQ_FP4) return DMOQ_EINVAL;
+
+  DMOQ_CHECK_ARG((is_down ? p.dn_idx : p.gu_idx) && (is_down ? p.dn_norm : p.gu_norm));
+  DMOQ_CHECK_ARG(a_stride >= (is_down ? p.inter : hidden) && a_stride % kG == 0);
+  if (use_tc_path() && dmoq_tc_supported(p, is_down, hidden))
+    return dmoq_grouped_gemm_tc(route, p, pool_index, is_down, epilogue, hidden, a_codes, a_scales, a_stride, out,
+                                out_stride, partials, static_cast<cudaStream_t>(stream));
 
   GemmArgs a{};
   a.tiles = reinterpret_cast<const DmoqTile*>(route->tiles);

@@ -181,6 +181,13 @@ int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* pools_host, 
                       void* out, int32_t out_stride, int32_t* partials, void* stream);
 
 /*
+ * Status word of the tensor-core (tcgen05) GEMM kernels on the current device, copied to the host
+ * (synchronises the device).  0 = healthy; bit 0 = a bounded mbarrier wait ran out, the launch that hit
+ * it wrote unspecified output.  No reference counterpart: the reference has no device-side waits.
+ */
+int dmoq_tc_status(int32_t* status_host);
+
+/*
  * Deterministic combine: y[t] = bf16( sum_slots dn[row_of[t*top_k+slot]] (+ dn[shared row of t]) ),
  * accumulated in fp32 in slot order.  Replaces final_hidden_states.index_add_
  * (quantization/wxa16/bit_partitioned_moe.py:966) and the shared-expert add (:1101-1106).

@@ -431,3 +431,11 @@ def test_packed_linear_vs_dense():
             cls.from_wxa16(q)
         y = q.to(DEV)(x.to(DEV))
         assert y.dtype == torch.bfloat16 and rel_fro(y.float().cpu().numpy(), want.detach().numpy()) < tol + 1e-2
+
+
+def test_zz_tensor_core_status_word_is_clean():
+    """No bounded wait of the tcgen05 kernels ran out during this session."""
+    import ctypes
+    st = ctypes.c_int32(-1)
+    _lib.check(_lib.load().dmoq_tc_status(ctypes.byref(st)), "dmoq_tc_status")
+    assert st.value == 0
