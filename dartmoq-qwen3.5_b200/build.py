@@ -12,6 +12,7 @@ LIB = os.path.join(HERE, "libdmoq.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC"]
+PER_FILE_FLAGS = {}
 
 
 def _sources():
@@ -36,7 +37,8 @@ def build(verbose: bool = False, force: bool = False) -> str:
         src, obj = pair
         if not force and not _stale(obj, [src] + headers):
             return
-        cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+        cmd = ([NVCC] + FLAGS + PER_FILE_FLAGS.get(os.path.basename(src), []) +
+               (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj])
         res = subprocess.run(cmd, capture_output=True, text=True)
         if verbose or res.returncode != 0:
             sys.stderr.write(res.stdout + res.stderr)

@@ -46,5 +46,5 @@ struct DmoqTile {
   int32_t expert;
   int32_t row0;
   int32_t rows;
-  int32_t pool;
+  int32_t rank;   // member rank of the expert inside its pool
 };

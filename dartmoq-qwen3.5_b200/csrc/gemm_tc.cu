@@ -6,9 +6,13 @@
 //               routing-weight epilogue through a padded shared-memory staging tile
 //   warps 8-11  producers: gather activation-code rows with cp.async straight into the 128B-swizzled
 //               K-major operand tile; copy the packed codebook indices with cp.async into a raw ring
-//               and expand them in registers (byte-permute lookups) into the swizzled B operand tile
+//               and expand them in registers (byte-permute lookups) into the swizzled B operand tile;
+//               they also stage each group's row scales and column norms into a small ring
 //   warp 12     one elected thread issues tcgen05.mma (M=128, N=128, K=32 x4 per 128-wide group),
 //               tcgen05.commit releases the smem stage and publishes the accumulator
+//   warps 13-15 idle (they only give their registers away: setmaxnreg moves them to the epilogue)
+// Tile metadata and row indices of the NEXT work item are fetched while the current one runs, so the
+// operand pipeline does not drain at item boundaries.
 // Accumulators are double-buffered in TMEM (2 x 128 columns), so the tensor pipe works on group g+1
 // while the epilogue warps scale group g.  Integer group sums are exact (kind::i8, int32), which is
 // what turboquant_utils/triton_kernels_a8.py:893-929 computes; kind::f8f6f4 gives the fp32 group sums of
@@ -24,12 +28,17 @@ constexpr int kBM = 128, kBN = 128, kG = DMOQ_GROUP;
 constexpr int kStages = 4;       // operand ring depth (one 128-wide group per stage)
 constexpr int kLag = 2;          // producer: stages between issuing the async copies and expanding them
 constexpr int kEpiWarps = 8, kProdWarps = 4;
-constexpr int kThreads = 32 * (kEpiWarps + kProdWarps + 1);
-constexpr int kGMax = 24;        // groups along K per member supported by the scale tiles (K <= 3072)
+constexpr int kThreads = 512;     // 4 warpgroups: epilogue, epilogue, producers, MMA (+3 idle warps)
+constexpr int kScaleRing = 8;     // per-group scale slots; must exceed kStages + 2 (see the epilogue)
+constexpr int kRegsEpi = 176, kRegsProd = 104, kRegsMma = 40;   // 256*176 + 128*104 + 128*40 <= 65536
 constexpr int kTileB = kBM * kG; // bytes of one int8 / e4m3 operand tile
 constexpr int kOutPitch = 272;   // bytes per staged output row (256 + 16: conflict-free 16-byte stores)
 constexpr uint32_t kSpinLimit = 1u << 26;
 constexpr long long kWaitCycles = 2000000000LL;
+// INT8 accumulators start from the bit pattern of 1.5*2^23: the int32 sum read back as fp32 is then
+// 12582912 + sum exactly (|sum| <= 128*127*127 < 2^22), which saves the integer->float conversion.
+constexpr uint32_t kMagicBits = 0x4B400000u;
+constexpr float kMagicFloat = 12582912.0f;
 
 __device__ int g_dmoq_tc_status = 0;
 
@@ -122,6 +131,40 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 32 lanes x 32 columns of one 32-bit value
+__device__ __forceinline__ void tc_st32_fill(uint32_t taddr, uint32_t v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};"
+      ::"r"(taddr), "r"(v)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// packed fp32 pairs (each lane IEEE round-to-nearest, unfused)
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
 __device__ __forceinline__ void bar_sync_epi() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory"); }
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t d;
@@ -200,12 +243,17 @@ struct Smem {
   uint8_t b[kStages][kTileB];
   uint8_t raw[kStages][kBN * 64];   // packed indices of one group (<= 64 bytes per row: 4-bit)
   uint8_t out[kBM * kOutPitch];
-  float norm[kGMax * kBN];
-  float xs[kGMax * kBM];
-  uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
+  float sc_norm[kScaleRing][kBN];   // column norms of a group, tile column order
+  float sc_xs[kScaleRing][kBM];     // row scales of a group
+  uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2], sc_full[kScaleRing];
   uint32_t tmem_base;
   int abort_flag;
 };
+
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 template <int MODE, int BIT, int EPI>
 __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
@@ -215,6 +263,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
   volatile int* abort_flag = &S.abort_flag;
   constexpr int BPG = 16 * BIT;                       // packed bytes per row per group
   constexpr int RAWB = (BIT == 1) ? 4 : BPG / 8;      // bytes one cp.async moves (1-bit: two chunks at once)
+  constexpr int kMmaWarp = kEpiWarps + kProdWarps;
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -225,10 +274,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       mbar_init(&S.acc_full[b], 1);
       mbar_init(&S.acc_empty[b], kEpiWarps);
     }
+    for (int i = 0; i < kScaleRing; ++i) mbar_init(&S.sc_full[i], kProdWarps);
     S.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == kEpiWarps + kProdWarps) {  // the MMA warp owns the TMEM allocation
+  if (warp == kMmaWarp) {  // the MMA warp owns the TMEM allocation
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&S.tmem_base)),
                  "r"(2 * kBN));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
@@ -237,6 +287,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = S.tmem_base;
+  if (MODE == DMOQ_A8) {
+    if (warp < kEpiWarps) {  // bias both accumulator buffers
+      const uint32_t t0 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (warp >> 2) * 64;
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {
+        tc_st32_fill(t0 + b * kBN, kMagicBits);
+        tc_st32_fill(t0 + b * kBN + 32, kMagicBits);
+      }
+      tc_wait_st();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+  }
 
   const int n_tiles = a.n_tiles[a.pool];
   const DmoqTile* tiles = a.tiles + a.n_tiles[DMOQ_MAX_POOLS + a.pool];
@@ -244,84 +308,96 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
   const int G = a.is_down ? a.inter / kG : a.hidden / kG;
   const int n_total = a.is_down ? a.hidden : a.n_members * 2 * a.inter;
   const int n_work = n_tiles * NB;
+  const int stride_w = gridDim.x;
+  const int n_items = (int)blockIdx.x < n_work ? (n_work - 1 - (int)blockIdx.x) / stride_w + 1 : 0;
+  const DmoqTile kNoTile{0, 0, 0, 0};
+  auto tile_of = [&](int item) {   // item index of this CTA -> tile record (clamped past the end)
+    const int w = blockIdx.x + item * stride_w;
+    return (item < n_items) ? tiles[w / NB] : kNoTile;
+  };
 
   if (warp < kEpiWarps) {
     // =========================================================================== epilogue warps
+    reg_inc<kRegsEpi>();
     const int quarter = warp & 3, half = warp >> 2;
     const int r = quarter * 32 + lane;               // tile row == TMEM lane
     const int etid = warp * 32 + lane;
-    uint32_t ia = 0;                                  // accumulator uses so far
-    for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
-      const DmoqTile tile = tiles[w / NB];
-      const int nb = w % NB;
-      const int rank = a.expert_rank[tile.expert];
-      const int gg0 = a.is_down ? rank * G : 0;
-      const int seg0 = a.is_down ? nb * kBN : rank * 2 * a.inter + nb * (kBN / 2);
-      const int seg1 = a.is_down ? seg0 : seg0 + a.inter;
+    uint32_t ia = 0;                                  // groups consumed so far
+    DmoqTile next = tile_of(0);
+    for (int item = 0; item < n_items; ++item) {
+      const DmoqTile tile = next;
+      next = tile_of(item + 1);                       // in flight while this item is processed
+      const int nb = (blockIdx.x + item * stride_w) % NB;
       const bool row_ok = r < tile.rows;
       const int grow = tile.row0 + r;
-      const int arow = row_ok ? (a.a_row ? a.a_row[grow] : grow) : -1;
+      float wgt = 0.f;
+      if (EPI == DMOQ_EPI_WEIGHTED && row_ok) wgt = a.row_weight[grow];
 
-      bar_sync_epi();  // the previous item's readers of norm / out are done
-      for (int i = etid; i < G * kBN; i += 32 * kEpiWarps) {
-        const int g = i / kBN, c = i % kBN;
-        const int n = a.is_down ? seg0 + c : ((c & 1) ? seg1 : seg0) + (c >> 1);
-        S.norm[i] = __half2float(reinterpret_cast<const __half*>(a.norm)[(size_t)(gg0 + g) * n_total + n]);
-      }
-      if (half == 0) {
-        for (int g = 0; g < G; ++g)
-          S.xs[g * kBM + r] =
-              row_ok ? __half2float(reinterpret_cast<const __half*>(a.a_scales)[(size_t)arow * (a.a_stride / kG) + g]) : 0.f;
-      }
-      bar_sync_epi();
-
-      float total[64];
+      float2 total2[32];
 #pragma unroll
-      for (int c = 0; c < 64; ++c) total[c] = 0.f;
+      for (int c = 0; c < 32; ++c) total2[c] = make_float2(0.f, 0.f);
 
       for (int g = 0; g < G; ++g, ++ia) {
         const uint32_t b = ia & 1, ph = (ia >> 1) & 1;
-        mbar_wait(&S.acc_full[b], ph, abort_flag);  // on a timeout the flag is raised and the data is void
+        const uint32_t slot = ia % kScaleRing;
+        // A scale slot is rewritten kScaleRing groups later; the producers can be at most kStages + 2 groups
+        // ahead of the group whose accumulator this warp has released, so the slot is still intact here.
+        mbar_wait(&S.sc_full[slot], (ia / kScaleRing) & 1, abort_flag);
+        mbar_wait(&S.acc_full[b], ph, abort_flag);    // on a timeout the flag is up and the data is void
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + b * kBN + half * 64;
-        const float xs = S.xs[g * kBM + r];
-        const float* nrm = &S.norm[g * kBN + half * 64];
+        const float xs = S.sc_xs[slot][r];
+        const float2 xs2 = make_float2(xs, xs);
+        const float2 unbias = make_float2(-kMagicFloat, -kMagicFloat);
+        const float4* nrm4 = reinterpret_cast<const float4*>(&S.sc_norm[slot][half * 64]);
         const int n_out = a.is_down ? a.hidden : 2 * a.inter;
 #pragma unroll
         for (int part = 0; part < 2; ++part) {   // two 32-column loads keep the register footprint down
           uint32_t v[32];
           tc_ld32(taddr + part * 32, v);
           tc_wait_ld();
+          if (MODE == DMOQ_A8) tc_st32_fill(taddr + part * 32, kMagicBits);  // re-arm the bias for the next use
           if (part == 1) {                         // the accumulator buffer can be overwritten now
+            if (MODE == DMOQ_A8) tc_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&S.acc_empty[b]);
           }
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const float f = (MODE == DMOQ_A8) ? (float)(int32_t)v[c] : __uint_as_float(v[c]);
-            total[part * 32 + c] = __fadd_rn(total[part * 32 + c], __fmul_rn(__fmul_rn(f, xs), nrm[part * 32 + c]));
+          for (int c4 = 0; c4 < 8; ++c4) {
+            const float4 nv = nrm4[part * 8 + c4];
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+              const int c = c4 * 4 + h2 * 2;
+              float2 f = make_float2(__uint_as_float(v[c]), __uint_as_float(v[c + 1]));
+              if (MODE == DMOQ_A8) f = add2(f, unbias);
+              const float2 n2 = h2 ? make_float2(nv.z, nv.w) : make_float2(nv.x, nv.y);
+              const int t = part * 16 + c4 * 2 + h2;
+              total2[t] = fma2(mul2(f, xs2), n2, total2[t]);   // (acc*xs)*norm + total, last step fused
+            }
           }
           if (MODE == DMOQ_A8 && a.partials != nullptr && row_ok) {
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
               const int col = half * 64 + part * 32 + c;
               const int n = a.is_down ? nb * kBN + col : (col & 1) * a.inter + nb * (kBN / 2) + (col >> 1);
-              a.partials[((size_t)grow * n_out + n) * G + g] = (int32_t)v[c];
+              a.partials[((size_t)grow * n_out + n) * G + g] = (int32_t)(v[c] - kMagicBits);
             }
           }
         }
       }
+
       // ---- tile epilogue through the staging tile
       if (EPI == DMOQ_EPI_SILU) {
         __align__(16) __half o[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float gate = __half2float(__float2half_rn(total[2 * i]));
-          const float up = __half2float(__float2half_rn(total[2 * i + 1]));
+          const float gate = __half2float(__float2half_rn(total2[i].x));
+          const float up = __half2float(__float2half_rn(total2[i].y));
           const float sg = __half2float(__float2half_rn(__fdiv_rn(gate, 1.0f + expf(-gate))));
           o[i] = __float2half_rn(__fmul_rn(sg, up));
         }
+        bar_sync_epi();  // the previous item's copy-out has finished reading the staging tile
 #pragma unroll
         for (int q = 0; q < 4; ++q)
           *reinterpret_cast<uint4*>(&S.out[r * kOutPitch + half * 64 + q * 16]) = reinterpret_cast<const uint4*>(o)[q];
@@ -340,15 +416,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
           for (int c = 0; c < 64; ++c) {
             const int col = half * 64 + c;
             const int n = (col & 1) * a.inter + nb * (kBN / 2) + (col >> 1);
-            out[(size_t)grow * a.out_stride + n] = __float2half_rn(total[c]);
+            out[(size_t)grow * a.out_stride + n] = __float2half_rn((c & 1) ? total2[c >> 1].y : total2[c >> 1].x);
           }
         }
       } else {
-        const float wgt = (EPI == DMOQ_EPI_WEIGHTED && row_ok) ? a.row_weight[grow] : 0.f;
         __align__(16) uint16_t o[64];
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
-          const __half h16 = __float2half_rn(total[c]);
+          const __half h16 = __float2half_rn((c & 1) ? total2[c >> 1].y : total2[c >> 1].x);
           if (EPI == DMOQ_EPI_WEIGHTED) {
             const __nv_bfloat16 bb = __float2bfloat16_rn(__half2float(h16));
             o[c] = __bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(__bfloat162float(bb), wgt)));
@@ -356,6 +431,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
             o[c] = __half_as_ushort(h16);
           }
         }
+        bar_sync_epi();
 #pragma unroll
         for (int q = 0; q < 8; ++q)
           *reinterpret_cast<uint4*>(&S.out[r * kOutPitch + half * 128 + q * 16]) = reinterpret_cast<const uint4*>(o)[q];
@@ -369,9 +445,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
         }
       }
     }
-  } else if (warp < kEpiWarps + kProdWarps) {
+  } else if (warp < kMmaWarp) {
     // =========================================================================== producer warps
-    const int pt = tid - 32 * kEpiWarps;              // 0..127
+    reg_dec<kRegsProd>();
+    const int pt = tid - 32 * kEpiWarps;              // 0..127: also the tile row / column whose scale it stages
     Lut lut;
 #pragma unroll
     for (int q = 0; q < 4; ++q) lut.w[q] = 0;
@@ -382,10 +459,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
     // stores fall on distinct shared-memory bank groups
     auto own_row = [&](int i) { return (BIT == 1) ? (pt >> 2) + 32 * (i >> 1) : (pt >> 3) + 16 * i; };
     auto own_chunk = [&](int i) { return (BIT == 1) ? 2 * (pt & 3) + (i & 1) : (pt & 7); };
+    const int xs_per_row = a.a_stride / kG;
 
-    uint32_t it = 0;       // stages issued
-    uint32_t done = 0;     // stages expanded and published
-    auto publish = [&](uint32_t j) {
+    // scale values travel in registers from the issue of a group to its publication kLag groups later
+    uint16_t xs_q[kLag + 1], nm_q[kLag + 1];
+#pragma unroll
+    for (int i = 0; i <= kLag; ++i) xs_q[i] = nm_q[i] = 0;
+
+    auto publish = [&](uint32_t j, int qi) {   // qi: position of group j's scales in the register queue
       const int s = j % kStages;
       if (BIT != 8) {
 #pragma unroll
@@ -413,34 +494,63 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
           *p = expand16<8>(raw, lut, true);
         }
       }
+      const uint32_t slot = j % kScaleRing;
+      uint16_t xs_h = xs_q[0], nm_h = nm_q[0];
+#pragma unroll
+      for (int i = 1; i <= kLag; ++i) {
+        if (qi == i) {
+          xs_h = xs_q[i];
+          nm_h = nm_q[i];
+        }
+      }
+      S.sc_xs[slot][pt] = __half2float(__ushort_as_half(xs_h));
+      S.sc_norm[slot][pt] = __half2float(__ushort_as_half(nm_h));
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&S.full[s]);
+      if (lane == 0) {
+        mbar_arrive(&S.sc_full[slot]);
+        mbar_arrive(&S.full[s]);
+      }
     };
 
-    for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
-      const DmoqTile tile = tiles[w / NB];
-      const int nb = w % NB;
-      const int rank = a.expert_rank[tile.expert];
-      const int gg0 = a.is_down ? rank * G : 0;
-      const int seg0 = a.is_down ? nb * kBN : rank * 2 * a.inter + nb * (kBN / 2);
-      const int seg1 = a.is_down ? seg0 : seg0 + a.inter;
-      // activation rows this thread copies: row (pt>>3) + 16*i, chunk pt&7
-      int arow[8];
+    // row bookkeeping of one work item: table rows this thread copies (8) and the row whose scale it stages
+    struct Rows {
+      int cp[8];
+      int own;
+    };
+    auto rows_of = [&](const DmoqTile& t) {
+      Rows rw;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int rr = (pt >> 3) + 16 * i;
-        const int grow = tile.row0 + rr;
-        arow[i] = rr < tile.rows ? (a.a_row ? a.a_row[grow] : grow) : -1;
+        rw.cp[i] = rr < t.rows ? (a.a_row ? a.a_row[t.row0 + rr] : t.row0 + rr) : -1;
       }
+      rw.own = pt < t.rows ? (a.a_row ? a.a_row[t.row0 + pt] : t.row0 + pt) : -1;
+      return rw;
+    };
+
+    uint32_t it = 0, done = 0;
+    DmoqTile t_next = tile_of(0), t_next2 = tile_of(1);
+    Rows r_next = rows_of(t_next);
+    for (int item = 0; item < n_items; ++item) {
+      const DmoqTile tile = t_next;
+      const Rows rw = r_next;
+      t_next = t_next2;
+      t_next2 = tile_of(item + 2);   // two items ahead: its rows are fetched one item ahead without a stall
+      r_next = rows_of(t_next);
+      const int nb = (blockIdx.x + item * stride_w) % NB;
+      const int gg0 = a.is_down ? tile.rank * G : 0;
+      const int seg0 = a.is_down ? nb * kBN : tile.rank * 2 * a.inter + nb * (kBN / 2);
+      const int seg1 = a.is_down ? seg0 : seg0 + a.inter;
+      const int own_n = a.is_down ? seg0 + pt : ((pt & 1) ? seg1 : seg0) + (pt >> 1);
       for (int g = 0; g < G; ++g, ++it) {
         const int s = it % kStages;
         mbar_wait(&S.empty[s], ((it / kStages) & 1) ^ 1, abort_flag);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int rr = (pt >> 3) + 16 * i, ch = pt & 7;
-          const uint8_t* src = a.a_codes + (size_t)(arow[i] < 0 ? 0 : arow[i]) * a.a_stride + (size_t)g * kG + ch * 16;
-          cp_async16_zfill(&S.a[s][swz128(rr, ch)], src, arow[i] >= 0);
+          const uint8_t* src = a.a_codes + (size_t)(rw.cp[i] < 0 ? 0 : rw.cp[i]) * a.a_stride + (size_t)g * kG + ch * 16;
+          cp_async16_zfill(&S.a[s][swz128(rr, ch)], src, rw.cp[i] >= 0);
         }
         if (BIT == 1) {
 #pragma unroll
@@ -460,29 +570,39 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
           }
         }
         cp_async_commit();
+        // scales of this group: loaded now, stored when the group is published
+#pragma unroll
+        for (int i = kLag; i > 0; --i) {
+          xs_q[i] = xs_q[i - 1];
+          nm_q[i] = nm_q[i - 1];
+        }
+        xs_q[0] = rw.own >= 0 ? a.a_scales[(size_t)rw.own * xs_per_row + g] : (uint16_t)0;
+        nm_q[0] = a.norm[(size_t)(gg0 + g) * n_total + own_n];
         if (it - done >= (uint32_t)kLag) {
           cp_async_wait<kLag>();
-          publish(done++);
+          publish(done++, kLag);
         }
       }
     }
     // drain: everything issued must be published so the MMA warp and the epilogue can finish
-    while (done < it) {
+    while (done < it) {   // the queue is not rotated any more: group j sits at position it-1-j
       const uint32_t pending = it - done - 1;
       if (pending >= 1) cp_async_wait<1>(); else cp_async_wait<0>();
-      publish(done++);
+      publish(done, (int)pending);
+      ++done;
     }
   } else {
-    // =========================================================================== MMA warp
-    constexpr uint32_t idesc_i8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-    constexpr uint32_t idesc_f8 = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-    uint32_t it = 0;
-    for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
-      for (int g = 0; g < G; ++g, ++it) {
+    reg_dec<kRegsMma>();
+    if (warp == kMmaWarp) {
+      // ========================================================================= MMA warp
+      constexpr uint32_t idesc_i8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      constexpr uint32_t idesc_f8 = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      const uint32_t total_groups = (uint32_t)n_items * (uint32_t)G;
+      for (uint32_t it = 0; it < total_groups; ++it) {
         const int s = it % kStages;
         const uint32_t b = it & 1;
         bool ok = mbar_wait(&S.full[s], (it / kStages) & 1, abort_flag);
-        ok = ok && mbar_wait(&S.acc_empty[b], ((it >> 1) & 1) ^ 1, abort_flag);
+        ok = mbar_wait(&S.acc_empty[b], ((it >> 1) & 1) ^ 1, abort_flag) && ok;
         tc_fence_after();
         if (lane == 0 && ok) {
           const uint64_t da = make_desc(smem_u32(&S.a[s][0]));
@@ -490,7 +610,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
           const uint32_t d = tmem_base + b * kBN;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {  // K = 32 bytes per instruction: +2 in 16-byte units
-            if (MODE == DMOQ_A8) tc_mma_i8(d, da + 2 * k, db + 2 * k, idesc_i8, k > 0);
+            if (MODE == DMOQ_A8) tc_mma_i8(d, da + 2 * k, db + 2 * k, idesc_i8, 1);  // buffer holds the bias
             else tc_mma_f8(d, da + 2 * k, db + 2 * k, idesc_f8, k > 0);
           }
           tc_commit(&S.empty[s]);
@@ -504,7 +624,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
   // ---- teardown: all roles meet here, then the allocating warp releases TMEM
   tc_fence_before();
   __syncthreads();
-  if (warp == kEpiWarps + kProdWarps) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * kBN));
   }
@@ -554,7 +674,7 @@ bool dmoq_tc_supported(const dmoq_pool_t& p, int is_down, int hidden) {
   if (p.mode != DMOQ_A8 && p.mode != DMOQ_FP8) return false;
   if (p.bit == 8 && !(p.mode == DMOQ_A8 && p.identity_lut)) return false;
   const int G = is_down ? p.inter / kG : hidden / kG;
-  return G >= 1 && G <= kGMax;
+  return G >= 1;
 }
 
 int dmoq_grouped_gemm_tc(const dmoq_route_t* route, const dmoq_pool_t& p, int pool_index, int is_down, int epilogue,

@@ -98,7 +98,7 @@ __device__ void scan_and_tiles(const RouteArgs& a, int32_t* s_count /* E_tot+1 i
     int row0 = a.r.expert_rows[e];
     for (int m = 0; m < n; m += a.r.tile_m, ++slot) {
       if (slot >= a.r.tile_cap) break;
-      DmoqTile t{e, row0 + m, min(a.r.tile_m, n - m), p};
+      DmoqTile t{e, row0 + m, min(a.r.tile_m, n - m), a.r.expert_rank[e]};
       reinterpret_cast<DmoqTile*>(a.r.tiles)[slot] = t;
     }
   }

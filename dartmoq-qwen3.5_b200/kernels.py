@@ -143,7 +143,7 @@ class _HostRoute:
         tiles = []
         for e, (start, count, _s0, _sc) in enumerate(expert_info):
             for m in range(0, count, TILE_M):
-                tiles.append((e, start + m, min(TILE_M, count - m), 0))
+                tiles.append((e, start + m, min(TILE_M, count - m), int(ranks[e])))
         i32 = dict(dtype=torch.int32, device=device)
         self.tiles = torch.tensor(tiles if tiles else [(0, 0, 0, 0)], **i32).reshape(-1, 4).contiguous()
         self.n_tiles = torch.tensor([len(tiles)] + [0] * (2 * MAX_POOLS - 1), **i32)

@@ -105,7 +105,7 @@ typedef struct dmoq_route {
                                  pool p's list starts at pool_src_base[p]; size = sum of the
                                  non-hoisted pools' act_cap_rows                               */
   const int32_t* pool_src_base; /* (DMOQ_MAX_POOLS) static: first pool_src entry of each non-hoisted pool */
-  int32_t* tiles;             /* (tile_cap, 4): expert, first row, row count, pool             */
+  int32_t* tiles;             /* (tile_cap, 4): expert, first row, row count, member rank      */
   int32_t* n_tiles;           /* (2*DMOQ_MAX_POOLS) tiles per pool, then each pool's first tile  */
   int32_t tile_cap;
   const int32_t* pool_hoisted;/* (DMOQ_MAX_POOLS) static copy of dmoq_pool_t.hoisted           */
