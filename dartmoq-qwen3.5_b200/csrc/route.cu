@@ -244,3 +244,75 @@ extern "C" int dmoq_route_build(const dmoq_route_t* route, const int64_t* topk_i
   route_place_kernel<<<a.n_chunks + shared_blocks, 32, e_bytes, s>>>(a);
   return dmoq_launch_status();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Routing build for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc at all: code running between
+// cudaStreamBeginCapture and cudaStreamEndCapture, real-time serving loops that have frozen their
+// memory pools, or plugins whose host framework owns every allocation and hands out none for scratch.
+// dmoq_route_build needs a scratch buffer from its caller; this variant brings its own, a fixed
+// array in the library's device image.  Every GPU that loads libdmoq.so holds these 4 MiB until the
+// process exits.
+constexpr size_t kStaticRouteInts = (size_t)1 << 20;
+static __device__ __align__(256) int32_t g_route_scratch[kStaticRouteInts];
+
+namespace {
+// Device address of g_route_scratch per device ordinal.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use; the address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+int32_t* g_route_scratch_ptr[64] = {nullptr};
+
+int route_scratch_for_current_device(int32_t** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DMOQ_EDEVICE;
+  if (g_route_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_route_scratch) != cudaSuccess || p == nullptr) return DMOQ_EDEVICE;
+    g_route_scratch_ptr[dev] = static_cast<int32_t*>(p);
+  }
+  *out = g_route_scratch_ptr[dev];
+  return DMOQ_OK;
+}
+}  // namespace
+
+extern "C" size_t dmoq_route_static_max_bytes(void) { return kStaticRouteInts * sizeof(int32_t); }
+
+extern "C" int dmoq_route_build_static(const dmoq_route_t* route, const int64_t* topk_idx, const float* topk_w,
+                                       const float* shared_w, void* stream) {
+  DMOQ_CHECK_ARG(route && topk_idx && topk_w);
+  const dmoq_route_t& r = *route;
+  DMOQ_CHECK_ARG(r.T >= 0 && r.top_k > 0 && r.E > 0 && r.E <= 4096 && r.tile_m > 0);
+  DMOQ_CHECK_ARG(r.n_pools >= 0 && r.n_pools <= DMOQ_MAX_POOLS);
+  DMOQ_CHECK_ARG(r.expert_pool && r.expert_rank && r.expert_rows && r.sorted_tokens && r.sorted_weights);
+  DMOQ_CHECK_ARG(r.row_of && r.a_row && r.pool_rows && r.pool_src && r.pool_src_base && r.tiles && r.n_tiles);
+  DMOQ_CHECK_ARG(r.pool_hoisted);
+  // the same scratch size the allocating variant asks its caller for; larger problems are refused
+  const size_t need = dmoq_route_workspace_bytes(r.T, r.top_k, r.E);
+  if (need == 0 || need > dmoq_route_static_max_bytes()) return DMOQ_ESIZE;
+  int32_t* scratch = nullptr;
+  const int rc = route_scratch_for_current_device(&scratch);
+  if (rc != DMOQ_OK) return rc;
+
+  RouteArgs a;
+  a.r = r;
+  a.topk_idx = topk_idx;
+  a.topk_w = topk_w;
+  a.shared_w = shared_w;
+  a.n_flat = r.T * r.top_k;
+  a.n_chunks = dmoq_ceil_div(a.n_flat, kChunk);
+  if (a.n_chunks == 0) a.n_chunks = 1;
+  a.hist = scratch;
+  a.pool_row0 = a.hist + (size_t)a.n_chunks * r.E;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t e_bytes = (size_t)r.E * sizeof(int32_t);
+  if (a.n_chunks == 1 && (!r.has_shared || r.T <= 4 * kChunk)) {
+    route_fused_kernel<<<1, 1024, 2 * e_bytes + 16, s>>>(a);
+    return dmoq_launch_status();
+  }
+  route_hist_kernel<<<a.n_chunks, 256, e_bytes, s>>>(a);
+  route_scan_kernel<<<1, 1024, e_bytes + 16, s>>>(a);
+  const int shared_blocks = r.has_shared ? dmoq_ceil_div(r.T, kChunk) : 0;
+  route_place_kernel<<<a.n_chunks + shared_blocks, 32, e_bytes, s>>>(a);
+  return dmoq_launch_status();
+}

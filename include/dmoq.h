@@ -130,6 +130,25 @@ int dmoq_route_build(const dmoq_route_t* route, const int64_t* topk_idx, const f
                      const float* shared_w, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * dmoq_route_build for callers that cannot allocate device memory (no counterpart in the reference,
+ * whose routing runs as torch ops that allocate freely).  Who needs it: code that runs while a stream
+ * is being captured, serving loops that froze their memory pools, host frameworks that own all
+ * allocations and grant none for scratch.  The scratch dmoq_route_build takes from its caller lives
+ * here in a fixed array inside the library's device image: dmoq_route_static_max_bytes() bytes
+ * (4 MiB), held by every GPU that loads the library until the process exits.
+ *   - Problems whose dmoq_route_workspace_bytes(T, top_k, E) exceeds that size return DMOQ_ESIZE.
+ *   - The first call on each device looks up the array's device address (with that device current);
+ *     make that first call outside any stream capture.
+ *   - Nothing is allocated or freed, here or in any routine it calls.
+ *   - All calls on one GPU share the array.  No word has to start at zero (a call writes every word
+ *     before it reads it), but two calls that overlap on the GPU, e.g. on different streams, race.
+ * Arguments and results are those of dmoq_route_build without the workspace.
+ */
+size_t dmoq_route_static_max_bytes(void);
+int dmoq_route_build_static(const dmoq_route_t* route, const int64_t* topk_idx, const float* topk_w,
+                            const float* shared_w, void* stream);
+
+/*
  * Group rotation fused with activation quantisation
  * (turboquant_utils/triton_kernels_a8.py:429 int8, triton_kernels_fp8.py:128 e4m3,
  *  triton_kernels_fp4.py:1036 e2m1+e8m0; rotation.py:176 for the unquantised A16 case).
