@@ -1,0 +1,155 @@
+"""Expert parallelism: experts sharded over the ranks of one node, tokens data-parallel.
+
+The reference has no distributed code; this is the B200 scale-out of the same layer.  Rank ``r`` owns the
+experts ``[r*E/N, (r+1)*E/N)``.  One forward is
+
+    route (replicated router, local tokens)  ->  pack rows by destination rank
+    ->  all_to_all (counts, then rows)       ->  grouped expert compute on the owner
+    ->  all_to_all back                      ->  fixed-order fp32 sum of each token's top-k rows
+
+The exchange plumbing below is plain torch + ``torch.distributed`` and device agnostic (NCCL over
+NVLink on GPUs, gloo on CPUs for tests); the expert compute is a callback, on GPUs the libdmoq engine.
+Rows always land in the receiver's own memory before any kernel touches them.
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+
+class DispatchPlan:
+    """Where every (token, slot) pair goes and how to bring the answers back."""
+
+    def __init__(self, topk_idx: torch.Tensor, experts_per_rank: int, world: int):
+        T, k = topk_idx.shape
+        flat_e = topk_idx.reshape(-1)
+        dest = torch.div(flat_e, experts_per_rank, rounding_mode="floor")
+        # stable order: by destination rank, then by flat (token, slot) index -> deterministic
+        self.order = torch.sort(dest * (T * k) + torch.arange(T * k, device=dest.device))[1]
+        self.send_counts = torch.bincount(dest, minlength=world)
+        self.token = torch.div(self.order, k, rounding_mode="floor")
+        self.local_expert = flat_e[self.order] - dest[self.order] * experts_per_rank
+        self.T, self.k = T, k
+
+    def inverse(self) -> torch.Tensor:
+        inv = torch.empty_like(self.order)
+        inv[self.order] = torch.arange(self.order.numel(), device=self.order.device)
+        return inv
+
+
+def exchange_counts(send_counts: torch.Tensor, group=None) -> torch.Tensor:
+    recv = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv, send_counts, group=group)
+    return recv
+
+
+def all_to_all_rows(rows: torch.Tensor, send: list, recv: list, group=None) -> torch.Tensor:
+    out = rows.new_empty((sum(recv),) + tuple(rows.shape[1:]))
+    dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=recv, input_split_sizes=send, group=group)
+    return out
+
+
+def ep_forward(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, experts_per_rank: int,
+               local_compute: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
+               group=None) -> torch.Tensor:
+    """x (T, H) local tokens; ``local_compute(rows, local_expert, weight) -> (rows, H)`` runs on the owner and
+    returns each row's expert output already multiplied by its routing weight.  Returns (T, H) in x's dtype."""
+    world = dist.get_world_size(group)
+    plan = DispatchPlan(topk_idx, experts_per_rank, world)
+    recv_counts = exchange_counts(plan.send_counts, group)
+    send = plan.send_counts.tolist()          # the one host synchronisation of an EP forward
+    recv = recv_counts.tolist()
+    rows = all_to_all_rows(x[plan.token], send, recv, group)
+    meta = torch.stack([plan.local_expert.to(torch.float32), topk_w.reshape(-1)[plan.order].to(torch.float32)], 1)
+    meta = all_to_all_rows(meta, send, recv, group)
+    out_rows = local_compute(rows, meta[:, 0].to(torch.int64), meta[:, 1])
+    back = all_to_all_rows(out_rows, recv, send, group)
+    # back[i] answers send row i; put the rows in (token, slot) order and add the k slots in slot order
+    per_pair = back[plan.inverse()].reshape(plan.T, plan.k, x.shape[1]).float()
+    y = per_pair[:, 0]
+    for s in range(1, plan.k):
+        y = y + per_pair[:, s]
+    return y.to(x.dtype)
+
+
+class ExpertParallelMoE(torch.nn.Module):
+    """EP wrapper around a local ``Wx*BitPartitionedGroupMoE`` that holds only this rank's experts.
+
+    ``gate`` is the replicated router over ALL experts (tuple-returning or logits, as the local modules
+    accept); ``local_moe`` must have ``num_experts == experts_per_rank`` and no shared expert; a shared
+    expert, being token-local, is applied here through its packed Linear layers.
+    """
+
+    def __init__(self, gate, local_moe, num_experts: int, top_k: int, shared_expert=None,
+                 shared_expert_gate=None, group=None):
+        super().__init__()
+        self.gate, self.local_moe = gate, local_moe
+        self.num_experts, self.top_k = num_experts, top_k
+        self.shared_expert, self.shared_expert_gate = shared_expert, shared_expert_gate
+        self.group = group
+
+    def _local(self, rows, local_expert, weight):
+        if rows.shape[0] == 0:
+            return rows
+        eng = self.local_moe._get_engine(rows.device)
+        return eng.run(rows.contiguous(), weight.reshape(-1, 1), local_expert.reshape(-1, 1), None)
+
+    @torch.no_grad()
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        b, s, h = hidden_states.shape
+        x = hidden_states.reshape(-1, h).contiguous()
+        out = self.gate(x)
+        if isinstance(out, tuple):
+            _, w, idx = out
+        else:
+            w, idx = out.softmax(dim=-1).topk(self.top_k, dim=-1)
+        world = dist.get_world_size(self.group)
+        y = ep_forward(x, w, idx, self.num_experts // world, self._local, self.group)
+        if self.shared_expert is not None and self.shared_expert_gate is not None:
+            y = y + self.shared_expert(x) * torch.sigmoid(self.shared_expert_gate(x))
+        return y.reshape(b, s, h)
+
+
+@torch.no_grad()
+def shard_experts(moe, lo: int, hi: int):
+    """New module of the same class holding experts ``[lo, hi)`` of ``moe`` (top_k = 1: on the owner every
+    received row is routed to exactly one local expert).  Packed tensors are sliced, not re-quantised; the
+    down-side rotation seed is advanced to the first kept column group, so the rotations stay those of the
+    full layer (seed + 128 * global group)."""
+    from .moe import WxA16Weights
+
+    cls = type(moe)
+    out = cls(None, hi - lo, moe.hidden_size, moe.intermediate_size, 1, None, None)
+    out.enable_timing = False
+    out.enable_rotation_hoist = moe.enable_rotation_hoist
+    out.rotation_hoist_threshold = moe.rotation_hoist_threshold
+    offsets = moe._offsets_lists()
+    for bs, w in moe.bit_weights.items():
+        bit = int(bs)
+        off = offsets[bs]
+        s0, s1 = off[lo], off[hi]
+        if s1 == s0:
+            continue
+        gu, dn = w.gate_up_packed, w.down_packed
+        col0, col1 = s0 * bit // 8, s1 * bit // 8
+        new_gu = dict(gu)
+        new_gu.pop("indices_packed_gf", None)
+        new_gu["indices_packed"] = gu["indices_packed"][2 * s0:2 * s1].contiguous()
+        new_gu["norms"] = gu["norms"][2 * s0:2 * s1].contiguous()
+        new_gu["shape"] = (2 * (s1 - s0), gu["shape"][1])
+        new_dn = dict(dn)
+        new_dn["indices_packed"] = dn["indices_packed"][:, col0:col1].contiguous()
+        new_dn["norms"] = dn["norms"][:, s0 // 128:s1 // 128].contiguous()
+        new_dn["shape"] = (dn["shape"][0], s1 - s0)
+        new_dn["seed"] = int(dn["seed"]) + s0
+        nw = WxA16Weights(bit, moe.hidden_size)
+        nw.set_packed_data(new_gu, new_dn)
+        out.bit_weights[bs] = nw
+        local = [o - s0 for o in off[lo:hi + 1]]
+        out.expert_offsets[bs] = torch.tensor(local, dtype=torch.long)
+        out._expert_offsets_cpu[bs] = local
+        out.inter_size_by_bit[bit] = s1 - s0
+    out.bit_list = [b for b in moe.bit_list if str(b) in out.bit_weights]
+    return out
