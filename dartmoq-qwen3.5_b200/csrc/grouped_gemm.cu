@@ -19,8 +19,8 @@
 
 namespace {
 
-constexpr int kBM = 128, kBN = 128, kG = DMOQ_GROUP;
-constexpr int kThreads = 512;  // 16 warps: 4 (rows) x 4 (cols), warp tile 32 x 32
+constexpr int kBN = 128, kG = DMOQ_GROUP;
+constexpr int kThreads = 512;  // 16 warps; 128-row tiles: 4 x 4 warps of 32 x 32, 32-row tiles: 2 x 8 warps of 16 x 16
 
 struct GemmArgs {
   const DmoqTile* tiles;
@@ -88,7 +88,7 @@ struct Traits {
   static constexpr int ES = (MODE == DMOQ_A8 || MODE == DMOQ_FP8) ? 1 : 2;  // operand element bytes in smem
   static constexpr int SG = (MODE == DMOQ_FP4) ? 32 : 128;                  // K elements per scale block
   static constexpr int ROWB = kG * ES;                                      // smem bytes per operand row
-  static constexpr int TILEB = kBM * ROWB;                                  // one operand tile
+  static constexpr int TILEB = kBN * ROWB;                                  // one weight operand tile
 };
 
 // swizzled byte offset of 16-byte chunk `c` of row `r`
@@ -97,8 +97,13 @@ __device__ __forceinline__ uint32_t swz(int r, int c) {
   return (uint32_t)(r * ROWB + ((c ^ (r & 7)) << 4));
 }
 
-template <int MODE, int BIT, int EPI>
+template <int MODE, int BIT, int EPI, int BM>
 __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
+  constexpr int kBM = BM;
+  constexpr int WN = (BM == 128) ? 4 : 8;          // warps along the columns
+  constexpr int MT = (BM == 128) ? 2 : 1;          // 16-row MMA tiles per warp
+  constexpr int NT = (BM == 128) ? 4 : 2;          // 8-column MMA tiles per warp
+  constexpr int TILEA = BM * Traits<MODE>::ROWB;   // one activation operand tile
   using T = Traits<MODE>;
   using Acc = typename Mma<MODE>::Acc;
   constexpr int ES = T::ES, ROWB = T::ROWB, TILEB = T::TILEB;
@@ -110,15 +115,15 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
   constexpr int KSTEPS_BLK = T::SG * ES / 32;
 
   extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t* s_a = smem;                                   // 2 x TILEB
-  uint8_t* s_b = smem + 2 * TILEB;                       // 2 x TILEB
-  float* s_norm = reinterpret_cast<float*>(smem + 4 * TILEB);       // 2 x 128
+  uint8_t* s_a = smem;                                   // 2 x TILEA
+  uint8_t* s_b = smem + 2 * TILEA;                       // 2 x TILEB
+  float* s_norm = reinterpret_cast<float*>(smem + 2 * TILEA + 2 * TILEB);   // 2 x 128
   float* s_rs = s_norm + 2 * kBN;                                    // 2 x 128 x 4
   int32_t* s_arow = reinterpret_cast<int32_t*>(s_rs + 2 * kBM * 4);  // 128
   uint8_t* s_blut = reinterpret_cast<uint8_t*>(s_arow + kBM);        // 256 x EB
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int wm = warp >> 2, wn = warp & 3;
+  const int wm = warp / WN, wn = warp % WN;
 
   // ---- byte -> expanded elements table
   for (int byte = tid; byte < 256; byte += kThreads) {
@@ -173,7 +178,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
     auto issue_loads = [&](int g, int buf) {
       // activation codes
       if (MODE == DMOQ_FP4) {
-        const int ar = s_arow[bj];
+        const int ar = bj < kBM ? s_arow[bj] : -1;
         if (ar >= 0) raw_a4 = *reinterpret_cast<const uint4*>(a.a_codes + (size_t)ar * (a.a_stride / 2) + g * (kG / 2) + bq * 16);
         else raw_a4 = make_uint4(0, 0, 0, 0);
       } else {
@@ -182,7 +187,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
           const int r = c / CH, ch = c % CH;
           const int ar = s_arow[r];
           const uint8_t* src = a.a_codes + ((size_t)(ar < 0 ? 0 : ar) * a.a_stride + (size_t)g * kG) * ES + ch * 16;
-          cp_async16_zfill(s_a + buf * TILEB + swz<ROWB>(r, ch), src, ar >= 0);
+          cp_async16_zfill(s_a + buf * TILEA + swz<ROWB>(r, ch), src, ar >= 0);
         }
       }
       cp_async_commit();
@@ -237,22 +242,22 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
 #pragma unroll
       for (int c = 0; c < 2 * ES; ++c)
         *reinterpret_cast<uint4*>(s_b + buf * TILEB + swz<ROWB>(bj, bq * 2 * ES + c)) = reinterpret_cast<const uint4*>(ob)[c];
-      if (MODE == DMOQ_FP4) {
+      if (MODE == DMOQ_FP4 && bj < kBM) {
         __align__(16) uint16_t oa[32];
         const uint32_t words[4] = {raw_a4.x, raw_a4.y, raw_a4.z, raw_a4.w};
 #pragma unroll
         for (int i = 0; i < 32; ++i) oa[i] = kE2M1Half[(words[i >> 3] >> (4 * (i & 7))) & 15];
 #pragma unroll
         for (int c = 0; c < 4; ++c)
-          *reinterpret_cast<uint4*>(s_a + buf * TILEB + swz<ROWB>(bj, bq * 4 + c)) = reinterpret_cast<const uint4*>(oa)[c];
+          *reinterpret_cast<uint4*>(s_a + buf * TILEA + swz<ROWB>(bj, bq * 4 + c)) = reinterpret_cast<const uint4*>(oa)[c];
       }
     };
 
-    float total[2][4][4];
+    float total[MT][NT][4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < MT; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+      for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int q = 0; q < 4; ++q) total[i][j][q] = 0.f;
 
@@ -265,46 +270,46 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
       const int buf = g & 1;
       if (g + 1 < G) issue_loads(g + 1, buf ^ 1);
 
-      const uint32_t a_base = smem_u32(s_a + buf * TILEB);
+      const uint32_t a_base = smem_u32(s_a + buf * TILEA);
       const uint32_t b_base = smem_u32(s_b + buf * TILEB);
       const int mat = lane >> 3, rr = lane & 7;
 #pragma unroll
       for (int blk = 0; blk < NBLK; ++blk) {
-        Acc acc[2][4][4];
+        Acc acc[MT][NT][4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i)
+        for (int i = 0; i < MT; ++i)
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
+          for (int j = 0; j < NT; ++j)
 #pragma unroll
             for (int q = 0; q < 4; ++q) acc[i][j][q] = 0;
 #pragma unroll
         for (int ks = 0; ks < KSTEPS_BLK; ++ks) {
           const int kc = (blk * KSTEPS_BLK + ks) * 2;
-          uint32_t af[2][4], bf[2][4];
+          uint32_t af[MT][4], bf[NT / 2][4];
 #pragma unroll
-          for (int mt = 0; mt < 2; ++mt)
-            ldmatrix_x4(af[mt], a_base + swz<ROWB>(wm * 32 + mt * 16 + rr + (mat & 1) * 8, kc + (mat >> 1)));
+          for (int mt = 0; mt < MT; ++mt)
+            ldmatrix_x4(af[mt], a_base + swz<ROWB>(wm * (MT * 16) + mt * 16 + rr + (mat & 1) * 8, kc + (mat >> 1)));
 #pragma unroll
-          for (int np = 0; np < 2; ++np)
-            ldmatrix_x4(bf[np], b_base + swz<ROWB>(wn * 32 + np * 16 + rr + (mat >> 1) * 8, kc + (mat & 1)));
+          for (int np = 0; np < NT / 2; ++np)
+            ldmatrix_x4(bf[np], b_base + swz<ROWB>(wn * (NT * 8) + np * 16 + rr + (mat >> 1) * 8, kc + (mat & 1)));
 #pragma unroll
-          for (int mt = 0; mt < 2; ++mt)
+          for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
+            for (int nt = 0; nt < NT; ++nt)
               Mma<MODE>::run(acc[mt][nt], af[mt], bf[nt >> 1][(nt & 1) * 2], bf[nt >> 1][(nt & 1) * 2 + 1]);
         }
         // total += (acc * row_scale) * col_norm, unfused, group order
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
+        for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            const int r = wm * 32 + mt * 16 + (lane >> 2) + h * 8;
+            const int r = wm * (MT * 16) + mt * 16 + (lane >> 2) + h * 8;
             const float rs = s_rs[(buf * kBM + r) * 4 + blk];
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
+            for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
               for (int q = 0; q < 2; ++q) {
-                const int c = wn * 32 + nt * 8 + (lane & 3) * 2 + q;
+                const int c = wn * (NT * 8) + nt * 8 + (lane & 3) * 2 + q;
                 const float nv = s_norm[buf * kBN + c];
                 const float v = __fmul_rn(__fmul_rn((float)acc[mt][nt][h * 2 + q], rs), nv);
                 total[mt][nt][h * 2 + q] = __fadd_rn(total[mt][nt][h * 2 + q], v);
@@ -328,16 +333,16 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
     if (EPI == DMOQ_EPI_SILU) {
       __half* s_out = reinterpret_cast<__half*>(smem);  // 128 x 64
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const int r = wm * 32 + mt * 16 + (lane >> 2) + h * 8;
+          const int r = wm * (MT * 16) + mt * 16 + (lane >> 2) + h * 8;
 #pragma unroll
-          for (int nt = 0; nt < 4; ++nt) {
+          for (int nt = 0; nt < NT; ++nt) {
             const float gate = __half2float(__float2half_rn(total[mt][nt][h * 2 + 0]));
             const float up = __half2float(__float2half_rn(total[mt][nt][h * 2 + 1]));
             const float sg = __half2float(__float2half_rn(__fdiv_rn(gate, 1.0f + expf(-gate))));
-            s_out[r * 64 + wn * 16 + nt * 4 + (lane & 3)] = __float2half_rn(__fmul_rn(sg, up));
+            s_out[r * 64 + wn * (NT * 4) + nt * 4 + (lane & 3)] = __float2half_rn(__fmul_rn(sg, up));
           }
         }
       __syncthreads();
@@ -352,16 +357,16 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
       // un-fused gate_up output (R, 2*inter) fp16: column j of the tile is gate (even) / up (odd)
       __half* out = reinterpret_cast<__half*>(a.out);
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const int r = wm * 32 + mt * 16 + (lane >> 2) + h * 8;
+          const int r = wm * (MT * 16) + mt * 16 + (lane >> 2) + h * 8;
           if (r >= tile.rows) continue;
 #pragma unroll
-          for (int nt = 0; nt < 4; ++nt)
+          for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
-              const int c = wn * 32 + nt * 8 + (lane & 3) * 2 + q;
+              const int c = wn * (NT * 8) + nt * 8 + (lane & 3) * 2 + q;
               const int n = (c & 1) * a.inter + nb * (kBN / 2) + (c >> 1);
               out[(size_t)(tile.row0 + r) * a.out_stride + n] = __float2half_rn(total[mt][nt][h * 2 + q]);
             }
@@ -369,14 +374,14 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
     } else {
       uint16_t* s_out = reinterpret_cast<uint16_t*>(smem);  // 128 x 128
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const int r = wm * 32 + mt * 16 + (lane >> 2) + h * 8;
+          const int r = wm * (MT * 16) + mt * 16 + (lane >> 2) + h * 8;
           float wgt = 1.f;
           if (EPI == DMOQ_EPI_WEIGHTED) wgt = r < tile.rows ? a.row_weight[tile.row0 + r] : 0.f;
 #pragma unroll
-          for (int nt = 0; nt < 4; ++nt)
+          for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
               const __half h16 = __float2half_rn(total[mt][nt][h * 2 + q]);
@@ -387,7 +392,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
               } else {
                 bits = __half_as_ushort(h16);
               }
-              s_out[r * kBN + wn * 32 + nt * 8 + (lane & 3) * 2 + q] = bits;
+              s_out[r * kBN + wn * (NT * 8) + nt * 8 + (lane & 3) * 2 + q] = bits;
             }
         }
       __syncthreads();
@@ -402,45 +407,51 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
   }
 }
 
-template <int MODE>
+template <int MODE, int BM>
 constexpr size_t smem_bytes(int bit) {
-  return 4 * (size_t)Traits<MODE>::TILEB + (2 * kBN + 2 * kBM * 4) * sizeof(float) + kBM * sizeof(int32_t) +
+  return 2 * (size_t)Traits<MODE>::TILEB + 2 * (size_t)BM * Traits<MODE>::ROWB + (2 * kBN + 2 * BM * 4) * sizeof(float) +
+         BM * sizeof(int32_t) +
          256 * (size_t)(8 / bit) * Traits<MODE>::ES + 128;
 }
 
-template <int MODE, int BIT, int EPI>
+template <int MODE, int BIT, int EPI, int BM>
 int launch(const GemmArgs& a, int work_cap, cudaStream_t s) {
   static bool configured = false;
-  const size_t bytes = smem_bytes<MODE>(BIT);
+  const size_t bytes = smem_bytes<MODE, BM>(BIT);
   if (!configured) {
-    if (cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BIT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
+    if (cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BIT, EPI, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
       return DMOQ_ELAUNCH;
     configured = true;
   }
   int grid = dmoq_sm_count();
   if (grid > work_cap) grid = work_cap;
   if (grid < 1) grid = 1;
-  grouped_gemm_kernel<MODE, BIT, EPI><<<grid, kThreads, bytes, s>>>(a);
+  grouped_gemm_kernel<MODE, BIT, EPI, BM><<<grid, kThreads, bytes, s>>>(a);
   return dmoq_launch_status();
 }
 
+template <int MODE, int BIT, int EPI>
+int launch_bm(const GemmArgs& a, int bm, int work_cap, cudaStream_t s) {
+  return bm == 128 ? launch<MODE, BIT, EPI, 128>(a, work_cap, s) : launch<MODE, BIT, EPI, 32>(a, work_cap, s);
+}
+
 template <int MODE, int BIT>
-int launch_epi(const GemmArgs& a, int epi, int work_cap, cudaStream_t s) {
+int launch_epi(const GemmArgs& a, int epi, int bm, int work_cap, cudaStream_t s) {
   switch (epi) {
-    case DMOQ_EPI_SILU: return launch<MODE, BIT, DMOQ_EPI_SILU>(a, work_cap, s);
-    case DMOQ_EPI_WEIGHTED: return launch<MODE, BIT, DMOQ_EPI_WEIGHTED>(a, work_cap, s);
-    case DMOQ_EPI_PLAIN: return launch<MODE, BIT, DMOQ_EPI_PLAIN>(a, work_cap, s);
+    case DMOQ_EPI_SILU: return launch_bm<MODE, BIT, DMOQ_EPI_SILU>(a, bm, work_cap, s);
+    case DMOQ_EPI_WEIGHTED: return launch_bm<MODE, BIT, DMOQ_EPI_WEIGHTED>(a, bm, work_cap, s);
+    case DMOQ_EPI_PLAIN: return launch_bm<MODE, BIT, DMOQ_EPI_PLAIN>(a, bm, work_cap, s);
     default: return DMOQ_EINVAL;
   }
 }
 
 template <int MODE>
-int launch_bit(const GemmArgs& a, int bit, int epi, int work_cap, cudaStream_t s) {
+int launch_bit(const GemmArgs& a, int bit, int epi, int bm, int work_cap, cudaStream_t s) {
   switch (bit) {
-    case 1: return launch_epi<MODE, 1>(a, epi, work_cap, s);
-    case 2: return launch_epi<MODE, 2>(a, epi, work_cap, s);
-    case 4: return launch_epi<MODE, 4>(a, epi, work_cap, s);
-    case 8: return launch_epi<MODE, 8>(a, epi, work_cap, s);
+    case 1: return launch_epi<MODE, 1>(a, epi, bm, work_cap, s);
+    case 2: return launch_epi<MODE, 2>(a, epi, bm, work_cap, s);
+    case 4: return launch_epi<MODE, 4>(a, epi, bm, work_cap, s);
+    case 8: return launch_epi<MODE, 8>(a, epi, bm, work_cap, s);
     default: return DMOQ_EINVAL;
   }
 }
@@ -469,7 +480,7 @@ extern "C" int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* p
                                  void* out, int32_t out_stride, int32_t* partials, void* stream) {
   DMOQ_CHECK_ARG(route && pools_host && a_codes && out);
   DMOQ_CHECK_ARG(pool_index >= 0 && pool_index < route->n_pools);
-  DMOQ_CHECK_ARG(route->tile_m == kBM);
+  DMOQ_CHECK_ARG(route->tile_m == 128 || route->tile_m == 32);
   const dmoq_pool_t& p = pools_host[pool_index];
   DMOQ_CHECK_ARG(p.inter > 0 && p.inter % kG == 0 && hidden > 0 && hidden % kG == 0);
   DMOQ_CHECK_ARG(p.identity_lut || (is_down ? p.dn_lut : p.gu_lut));
@@ -480,7 +491,7 @@ extern "C" int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* p
 
   DMOQ_CHECK_ARG((is_down ? p.dn_idx : p.gu_idx) && (is_down ? p.dn_norm : p.gu_norm));
   DMOQ_CHECK_ARG(a_stride >= (is_down ? p.inter : hidden) && a_stride % kG == 0);
-  if (use_tc_path() && dmoq_tc_supported(p, is_down, hidden))
+  if (route->tile_m == 128 && use_tc_path() && dmoq_tc_supported(p, is_down, hidden))
     return dmoq_grouped_gemm_tc(route, p, pool_index, is_down, epilogue, hidden, a_codes, a_scales, a_stride, out,
                                 out_stride, partials, static_cast<cudaStream_t>(stream));
 
@@ -513,10 +524,10 @@ extern "C" int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* p
   const int work_cap = cap > (1 << 30) ? (1 << 30) : (int)cap;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (p.mode) {
-    case DMOQ_A16: return launch_bit<DMOQ_A16>(a, p.bit, epilogue, work_cap, s);
-    case DMOQ_A8: return launch_bit<DMOQ_A8>(a, p.bit, epilogue, work_cap, s);
-    case DMOQ_FP8: return launch_bit<DMOQ_FP8>(a, p.bit, epilogue, work_cap, s);
-    case DMOQ_FP4: return launch_bit<DMOQ_FP4>(a, p.bit, epilogue, work_cap, s);
+    case DMOQ_A16: return launch_bit<DMOQ_A16>(a, p.bit, epilogue, route->tile_m, work_cap, s);
+    case DMOQ_A8: return launch_bit<DMOQ_A8>(a, p.bit, epilogue, route->tile_m, work_cap, s);
+    case DMOQ_FP8: return launch_bit<DMOQ_FP8>(a, p.bit, epilogue, route->tile_m, work_cap, s);
+    case DMOQ_FP4: return launch_bit<DMOQ_FP4>(a, p.bit, epilogue, route->tile_m, work_cap, s);
     default: return DMOQ_EINVAL;
   }
 }

@@ -42,6 +42,7 @@ __device__ void scan_and_tiles(const RouteArgs& a, int32_t* s_count /* E_tot+1 i
   const int E_tot = E + a.r.has_shared;
   const int P = a.r.n_pools;
   __shared__ int32_t s_tile_base[DMOQ_MAX_POOLS];
+  __shared__ int8_t s_pool[4100];   // pool of each expert, staged once: the serial scan below must not wait on HBM
 
   // rows per expert; chunk histograms become exclusive chunk offsets
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -53,6 +54,10 @@ __device__ void scan_and_tiles(const RouteArgs& a, int32_t* s_count /* E_tot+1 i
     }
     s_count[e] = run;
   }
+  for (int e = threadIdx.x; e < E_tot; e += blockDim.x) {
+    const int p = a.r.expert_pool[e];
+    s_pool[e] = (int8_t)((p >= 0 && p < P) ? p : -1);
+  }
   if (threadIdx.x == 0 && a.r.has_shared) s_count[E] = a.r.T;
   __syncthreads();
 
@@ -61,11 +66,11 @@ __device__ void scan_and_tiles(const RouteArgs& a, int32_t* s_count /* E_tot+1 i
     for (int p = 0; p < DMOQ_MAX_POOLS; ++p) pool_rows[p] = pool_tiles[p] = 0;
     int run = 0;
     for (int e = 0; e < E_tot; ++e) {
-      int n = s_count[e];
+      const int n = s_count[e];
       a.r.expert_rows[e] = run;
       run += n;
-      int p = a.r.expert_pool[e];
-      if (p >= 0 && p < P) {
+      const int p = s_pool[e];
+      if (p >= 0) {
         a.pool_row0[e] = pool_rows[p];
         pool_rows[p] += n;
         pool_tiles[p] += (n + a.r.tile_m - 1) / a.r.tile_m;
@@ -86,19 +91,21 @@ __device__ void scan_and_tiles(const RouteArgs& a, int32_t* s_count /* E_tot+1 i
   __syncthreads();
 
   // tile lists: pool p's tiles are contiguous from s_tile_base[p], experts in index order.
-  // Each thread walks the experts before its own to find its first tile slot.
+  // Each thread walks the experts before its own to find its first tile slot and first row.
   for (int e = threadIdx.x; e < E_tot; e += blockDim.x) {
-    int p = a.r.expert_pool[e];
-    if (p < 0 || p >= P) continue;
-    int n = s_count[e];
+    const int p = s_pool[e];
+    if (p < 0) continue;
+    const int n = s_count[e];
     if (n == 0) continue;
-    int slot = s_tile_base[p];
-    for (int q = 0; q < e; ++q)
-      if (a.r.expert_pool[q] == p) slot += (s_count[q] + a.r.tile_m - 1) / a.r.tile_m;
-    int row0 = a.r.expert_rows[e];
+    int slot = s_tile_base[p], row0 = 0;
+    for (int q = 0; q < e; ++q) {
+      row0 += s_count[q];
+      if (s_pool[q] == p) slot += (s_count[q] + a.r.tile_m - 1) / a.r.tile_m;
+    }
+    const int rank = a.r.expert_rank[e];
     for (int m = 0; m < n; m += a.r.tile_m, ++slot) {
       if (slot >= a.r.tile_cap) break;
-      DmoqTile t{e, row0 + m, min(a.r.tile_m, n - m), a.r.expert_rank[e]};
+      DmoqTile t{e, row0 + m, min(a.r.tile_m, n - m), rank};
       reinterpret_cast<DmoqTile*>(a.r.tiles)[slot] = t;
     }
   }

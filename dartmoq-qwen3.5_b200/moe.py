@@ -315,7 +315,10 @@ class _Engine:
         ws.a_row = torch.zeros(max(R, 1), **i32)
         ws.pool_rows = torch.zeros(MAX_POOLS, **i32)
         ws.n_tiles = torch.zeros(2 * MAX_POOLS, **i32)
-        ws.tile_cap = (R + TILE_M - 1) // TILE_M + n_entries
+        # small batches (a few rows per expert) use 32-row tiles: every packed weight is still expanded once
+        # per expert, but far fewer padded rows go through the MMAs
+        ws.tile_m = 32 if (T <= 256 and T * self.k_v <= 8 * self.E_v) else TILE_M
+        ws.tile_cap = (R + ws.tile_m - 1) // ws.tile_m + n_entries
         ws.tiles = torch.zeros(ws.tile_cap, 4, **i32)
         bases, total = [], 0
         ws.act_codes, ws.act_scales = [], []
@@ -340,7 +343,7 @@ class _Engine:
         ws.dn = torch.empty(max(R, 1), self.hidden, dtype=torch.bfloat16, device=dev)
         r = Route()
         r.T, r.top_k, r.E = T, self.k_v, self.E_v
-        r.has_shared, r.tile_m, r.n_pools = int(self.has_shared), TILE_M, len(self.pools)
+        r.has_shared, r.tile_m, r.n_pools = int(self.has_shared), ws.tile_m, len(self.pools)
         r.expert_pool, r.expert_rank = self.expert_pool.data_ptr(), self.expert_rank.data_ptr()
         r.expert_rows = ws.expert_rows.data_ptr()
         r.sorted_tokens, r.sorted_weights = ws.sorted_tokens.data_ptr(), ws.sorted_weights.data_ptr()
@@ -442,7 +445,7 @@ class WxA16BitPartitionedGroupMoE(nn.Module):
     """Bit-partitioned MoE over packed weights, fp16 activations."""
 
     MODE = A16
-    _DEVICE_CACHE_ATTRS = ("_engine", "_bit_ctx_cache", "_bit_ctx_device")
+    _DEVICE_CACHE_ATTRS = ("_engine", "_bit_ctx_cache", "_bit_ctx_device", "_graphs")
 
     def __init__(self, gate, num_experts: int, hidden_size: int, intermediate_size: int, top_k: int = 6,
                  shared_expert=None, shared_expert_gate=None):
@@ -466,6 +469,10 @@ class WxA16BitPartitionedGroupMoE(nn.Module):
         self._expert_offsets_cpu: dict = {}
         self.bit_list: list = []
         self._engine: Optional[_Engine] = None
+        # small batches replay a captured CUDA graph of the expert path (no per-launch host cost)
+        self.enable_cuda_graph = True
+        self.cuda_graph_max_tokens = 256
+        self._graphs: Optional[dict] = None
 
     # ------------------------------------------------------------------ construction
     def _apply(self, fn, *args, **kwargs):
@@ -588,6 +595,37 @@ class WxA16BitPartitionedGroupMoE(nn.Module):
             self._engine = eng
         return eng
 
+    def _run_graphed(self, eng, x, topk_w, topk_idx, shared_w):
+        """First call for a token count runs eagerly (also finishes one-time kernel set-up); the second call
+        captures the whole expert path into a CUDA graph; later calls copy the inputs into the graph's static
+        buffers and replay it."""
+        if self._graphs is None:
+            self._graphs = {}
+        key = (x.shape[0], x.dtype, tuple(topk_idx.shape), shared_w is not None)
+        entry = self._graphs.get(key)
+        if entry is None:
+            self._graphs[key] = "warm"
+            return eng.run(x, topk_w, topk_idx, shared_w)
+        if entry == "warm":
+            if len(self._graphs) > 8:
+                self._graphs = {key: "warm"}
+            st = dict(x=x.clone(), w=topk_w.to(torch.float32).clone(), i=topk_idx.to(torch.int64).clone(),
+                      s=None if shared_w is None else shared_w.to(torch.float32).clone())
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                st["y"] = eng.run(st["x"], st["w"], st["i"], st["s"])
+            entry = (graph, st)
+            self._graphs[key] = entry
+        graph, st = entry
+        st["x"].copy_(x)
+        st["w"].copy_(topk_w)
+        st["i"].copy_(topk_idx)
+        if shared_w is not None:
+            st["s"].copy_(shared_w)
+        graph.replay()
+        return st["y"].clone()
+
     def set_cuda_profile(self, enabled: bool = True):
         """CUDA-event stage timing into ``last_cuda_stats`` (adds one synchronise per forward)."""
         self.enable_cuda_profile = bool(enabled)
@@ -626,7 +664,11 @@ class WxA16BitPartitionedGroupMoE(nn.Module):
             shared_w = torch.sigmoid(self.shared_expert_gate(x)).reshape(-1)
         if prof is not None:
             prof("router")
-        y = eng.run(x, topk_w, topk_idx, shared_w, prof=prof, partials=_partials)
+        if (self.enable_cuda_graph and prof is None and _partials is None
+                and x.shape[0] <= self.cuda_graph_max_tokens and not torch.cuda.is_current_stream_capturing()):
+            y = self._run_graphed(eng, x, topk_w, topk_idx, shared_w)
+        else:
+            y = eng.run(x, topk_w, topk_idx, shared_w, prof=prof, partials=_partials)
         if eng.shared_torch:
             y = y + self.shared_expert(x) * torch.sigmoid(self.shared_expert_gate(x))
         if prof is not None:

@@ -442,6 +442,28 @@ def test_packed_linear_vs_dense():
         assert y.dtype == torch.bfloat16 and rel_fro(y.float().cpu().numpy(), want.detach().numpy()) < tol + 1e-2
 
 
+@pytest.mark.parametrize("mode", ["wxa16", "wxa8"])
+def test_small_batch_graph_replay_matches_eager(mode):
+    """Decode regime: 32-row tiles and CUDA-graph replay give the eager result, call after call."""
+    moe = _layer(mode, seed=31, n_experts=16, top_k=4).to(DEV)
+    outs = []
+    for call in range(4):
+        x = synth.make_activations(6, 256, seed=40 + call % 2, device=DEV)
+        y = moe(x.unsqueeze(0))[0].clone()
+        moe.enable_cuda_graph = False
+        want = moe(x.unsqueeze(0))[0]
+        moe.enable_cuda_graph = True
+        assert torch.equal(y, want), call
+        outs.append(y)
+    assert moe._graphs and any(isinstance(v, tuple) for v in moe._graphs.values())
+    assert torch.equal(outs[0], outs[2]) and not torch.equal(outs[0], outs[1])
+    ref_moe = _layer(mode, seed=31, n_experts=16, top_k=4)
+    xc = synth.make_activations(6, 256, seed=40)
+    tw, ti, sw = routing(ref_moe, xc)
+    ref = O.moe_forward(to_oracle_layer(ref_moe), xc, tw, ti, sw)["y"]
+    assert rel_fro(outs[0].float().cpu().numpy(), ref) < TOL[mode]
+
+
 def test_zz_tensor_core_status_word_is_clean():
     """No bounded wait of the tcgen05 kernels ran out during this session."""
     import ctypes
