@@ -9,7 +9,10 @@
 //   e4m3       turboquant_utils/triton_kernels_fp8.py:128-187
 //   e2m1+e8m0  turboquant_utils/triton_kernels_fp4.py:1036-1104
 // and the unquantised fp16 output stands in for rotation.py:176 (batch_rotate_input).
+#include <cstdlib>
+
 #include "common.cuh"
+#include "rotq.cuh"
 
 namespace {
 
@@ -19,25 +22,6 @@ constexpr int kThreads = 128;   // 16 column groups x 8 row groups, 8x8 outputs 
 constexpr int kPPitch = kG + 4; // padded pitch of the transposed rotation (floats)
 constexpr int kXPitch = kRows + 4;
 
-struct RotArgs {
-  const void* x;
-  int src_is_bf16;
-  int K;                        // columns rotated (multiple of 128)
-  int x_stride, o_stride;       // row pitch (elements) of x and of the code table
-  const uint16_t* rot;          // fp16 (n_mats, 128, 128)
-  const int32_t* src_row;       // optional gather
-  int n_rows;
-  const int32_t* n_rows_dev;    // optional device-side row count
-  float extra_scale;
-  void* codes;
-  void* scales;
-  // tile-driven variant (down side)
-  const DmoqTile* tiles;
-  const int32_t* n_tiles;       // n_tiles[pool], n_tiles[8+pool] = first tile
-  const int32_t* expert_rank;
-  int pool;
-  int groups_per_member;
-};
 
 __device__ __forceinline__ void load_rotation(float* s_p, const uint16_t* rot_mat) {
   // s_p[k][j] = P[j][k]
@@ -253,6 +237,16 @@ int launch_tiles(const RotArgs& a, int tile_cap, cudaStream_t s) {
   return dmoq_launch_status();
 }
 
+// DMOQ_ROTQ=chain keeps every output on the CUDA-core FMA chain (A/B against the tensor-core kernel).
+bool use_mma_rotation() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* v = getenv("DMOQ_ROTQ");
+    cached = (v && v[0] == 'c') ? 0 : 1;
+  }
+  return cached == 1;
+}
+
 }  // namespace
 
 int dmoq_sm_count() {
@@ -290,6 +284,7 @@ extern "C" int dmoq_rotate_quant(int32_t mode, const void* x, int32_t src_is_bf1
   a.codes = codes;
   a.scales = scales;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (use_mma_rotation()) return dmoq_rotq_mma_rows(mode, a, s);
   switch (mode) {
     case DMOQ_A16: return launch_rows<DMOQ_A16>(a, s);
     case DMOQ_A8: return launch_rows<DMOQ_A8>(a, s);
@@ -324,6 +319,7 @@ extern "C" int dmoq_rotate_quant_down(const dmoq_route_t* route, const dmoq_pool
   a.pool = pool_index;
   a.groups_per_member = p.inter / kG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (use_mma_rotation()) return dmoq_rotq_mma_tiles(p.mode, a, route->tile_cap, s);
   switch (p.mode) {
     case DMOQ_A16: return launch_tiles<DMOQ_A16>(a, route->tile_cap, s);
     case DMOQ_A8: return launch_tiles<DMOQ_A8>(a, route->tile_cap, s);

@@ -111,48 +111,105 @@ __device__ void scan_and_tiles(const RouteArgs& a, int32_t* s_count /* E_tot+1 i
   }
 }
 
-// --- phase 3: stable placement of one chunk (one warp) ----------------------------------
-__device__ void place_chunk(const RouteArgs& a, int chunk, int32_t* s_running) {
+// --- phase 3: stable placement of one chunk ------------------------------------------------
+// The whole block first stages everything the placement reads (the chunk's entries, the chunk offsets,
+// the expert row prefix, the pool tables) in shared memory; warp 0 then walks the chunk in order, 32
+// entries at a time, so that no step of the serial walk waits on global memory.
+struct PlaceSmem {
+  int32_t* running;   // E
+  int32_t* offset;    // E       chunk offsets of this chunk
+  int32_t* rows;      // E + 2   expert row prefix
+  int32_t* prow0;     // E + 1   first activation-table row of each expert inside its pool
+  int32_t* entry;     // kChunk  expert of each entry (-1 = invalid)
+  float* weight;      // kChunk
+  int8_t* pool;       // E + 1 (+ padding)
+};
+
+__device__ PlaceSmem carve_place_smem(int32_t* base, int E) {
+  PlaceSmem m;
+  m.running = base;
+  m.offset = m.running + E;
+  m.rows = m.offset + E;
+  m.prow0 = m.rows + E + 2;
+  m.entry = m.prow0 + E + 1;
+  m.weight = reinterpret_cast<float*>(m.entry + kChunk);
+  m.pool = reinterpret_cast<int8_t*>(m.weight + kChunk);
+  return m;
+}
+
+__host__ __device__ inline size_t place_smem_bytes(int E) {
+  return (size_t)(4 * E + 3 + 2 * kChunk) * sizeof(int32_t) + (size_t)E + 8;
+}
+
+__device__ void place_chunk(const RouteArgs& a, int chunk, const PlaceSmem& m) {
   const int E = a.r.E;
-  const int lane = threadIdx.x & 31;
-  for (int e = lane; e < E; e += 32) s_running[e] = 0;
-  __syncwarp();
+  const int P = a.r.n_pools;
   const int lo = chunk * kChunk;
   const int hi = min(lo + kChunk, a.n_flat);
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    m.running[e] = 0;
+    m.offset[e] = a.hist[(size_t)chunk * E + e];
+    m.prow0[e] = a.pool_row0[e];
+    const int p = a.r.expert_pool[e];
+    m.pool[e] = (int8_t)((p >= 0 && p < P) ? p : -1);
+  }
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) m.rows[e] = a.r.expert_rows[e];
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const long long e64 = a.topk_idx[i];
+    m.entry[i - lo] = (e64 >= 0 && e64 < E) ? (int)e64 : -1;
+    m.weight[i - lo] = a.topk_w[i];
+  }
+  __syncthreads();
+  if (threadIdx.x >= 32) return;
+  const int lane = threadIdx.x;
+  int hoisted[DMOQ_MAX_POOLS], src_base[DMOQ_MAX_POOLS];
+#pragma unroll
+  for (int p = 0; p < DMOQ_MAX_POOLS; ++p) {
+    hoisted[p] = a.r.pool_hoisted[p];
+    src_base[p] = a.r.pool_src_base[p];
+  }
   for (int base = lo; base < hi; base += 32) {
     const int i = base + lane;
-    long long e64 = (i < hi) ? a.topk_idx[i] : -1;
-    const bool ok = (e64 >= 0 && e64 < E);
-    const int e = ok ? (int)e64 : -1 - lane;  // invalid lanes get unique keys
+    const int e_in = (i < hi) ? m.entry[i - lo] : -1;
+    const bool ok = e_in >= 0;
+    const int e = ok ? e_in : -1 - lane;  // invalid lanes get unique keys
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     const int before = __popc(peers & ((1u << lane) - 1));
     int start = 0;
-    if (ok) start = s_running[e];
+    if (ok) start = m.running[e];
     __syncwarp();
-    if (ok && before == 0) s_running[e] = start + __popc(peers);
+    if (ok && before == 0) m.running[e] = start + __popc(peers);
     __syncwarp();
     if (i < hi) {
       if (!ok) {
         a.r.row_of[i] = -1;
         continue;
       }
-      const int within = a.hist[(size_t)chunk * E + e] + start + before;
-      const int pos = a.r.expert_rows[e] + within;
+      const int within = m.offset[e] + start + before;
+      const int pos = m.rows[e] + within;
       const int tok = i / a.r.top_k;
-      const int p = a.r.expert_pool[e];
+      const int p = m.pool[e];
       a.r.sorted_tokens[pos] = tok;
-      a.r.sorted_weights[pos] = a.topk_w[i];
-      if (p < 0 || p >= a.r.n_pools) {
+      a.r.sorted_weights[pos] = m.weight[i - lo];
+      if (p < 0) {
         a.r.row_of[i] = -1;  // expert without weights contributes nothing
         a.r.a_row[pos] = 0;
       } else {
         a.r.row_of[i] = pos;
-        if (a.r.pool_hoisted[p]) {
+        int hs = 0, sb = 0;
+#pragma unroll
+        for (int q = 0; q < DMOQ_MAX_POOLS; ++q) {
+          if (q == p) {
+            hs = hoisted[q];
+            sb = src_base[q];
+          }
+        }
+        if (hs) {
           a.r.a_row[pos] = tok;
         } else {
-          const int tr = a.pool_row0[e] + within;
+          const int tr = m.prow0[e] + within;
           a.r.a_row[pos] = tr;
-          a.r.pool_src[a.r.pool_src_base[p] + tr] = tok;
+          a.r.pool_src[sb + tr] = tok;
         }
       }
     }
@@ -186,7 +243,7 @@ __global__ void route_scan_kernel(RouteArgs a) {
 __global__ void route_place_kernel(RouteArgs a) {
   extern __shared__ int32_t s_dyn[];
   if ((int)blockIdx.x < a.n_chunks) {
-    place_chunk(a, blockIdx.x, s_dyn);
+    place_chunk(a, blockIdx.x, carve_place_smem(s_dyn, a.r.E));
   } else if (a.r.has_shared) {
     const int b = blockIdx.x - a.n_chunks;
     place_shared(a, b * kChunk, min((b + 1) * kChunk, a.r.T));
@@ -195,16 +252,41 @@ __global__ void route_place_kernel(RouteArgs a) {
 
 // Small problems (one chunk): everything in a single block.
 __global__ void route_fused_kernel(RouteArgs a) {
-  extern __shared__ int32_t s_dyn[];  // [0, E): histogram / running, [E, 2E+2): counts
-  int32_t* s_hist = s_dyn;
-  int32_t* s_count = s_dyn + a.r.E;
-  chunk_histogram(a, 0, s_hist);
-  for (int e = threadIdx.x; e < a.r.E; e += blockDim.x) a.hist[e] = s_hist[e];
+  extern __shared__ int32_t s_dyn[];  // placement tables first, then E+2 counts
+  const PlaceSmem m = carve_place_smem(s_dyn, a.r.E);
+  int32_t* s_count = s_dyn + (place_smem_bytes(a.r.E) + 3) / 4;
+  chunk_histogram(a, 0, m.running);
+  for (int e = threadIdx.x; e < a.r.E; e += blockDim.x) a.hist[e] = m.running[e];
   __syncthreads();
   scan_and_tiles(a, s_count);
+  __threadfence_block();
   __syncthreads();
-  if (threadIdx.x < 32) place_chunk(a, 0, s_hist);
   if (a.r.has_shared) place_shared(a, 0, a.r.T);
+  place_chunk(a, 0, m);
+}
+
+// Shared launch sequence of both routing entry points.
+int launch_route(const RouteArgs& a, bool fused, cudaStream_t s) {
+  const dmoq_route_t& r = a.r;
+  const size_t e_bytes = (size_t)r.E * sizeof(int32_t);
+  const size_t place_bytes = place_smem_bytes(r.E) + 16;
+  const size_t fused_bytes = place_bytes + e_bytes + 16;
+  static bool configured = false;
+  if (!configured) {  // up to 4096 experts: the placement tables can exceed the default 48 KiB
+    if (cudaFuncSetAttribute(route_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(route_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess)
+      return DMOQ_ELAUNCH;
+    configured = true;
+  }
+  if (fused) {
+    route_fused_kernel<<<1, 1024, fused_bytes, s>>>(a);
+    return dmoq_launch_status();
+  }
+  route_hist_kernel<<<a.n_chunks, 256, e_bytes, s>>>(a);
+  route_scan_kernel<<<1, 1024, e_bytes + 16, s>>>(a);
+  const int shared_blocks = r.has_shared ? dmoq_ceil_div(r.T, kChunk) : 0;
+  route_place_kernel<<<a.n_chunks + shared_blocks, 128, place_bytes, s>>>(a);
+  return dmoq_launch_status();
 }
 
 }  // namespace
@@ -242,14 +324,9 @@ extern "C" int dmoq_route_build(const dmoq_route_t* route, const int64_t* topk_i
   const size_t e_bytes = (size_t)r.E * sizeof(int32_t);
 
   if (a.n_chunks == 1 && (!r.has_shared || r.T <= 4 * kChunk)) {
-    route_fused_kernel<<<1, 1024, 2 * e_bytes + 16, s>>>(a);
-    return dmoq_launch_status();
+    return launch_route(a, true, s);
   }
-  route_hist_kernel<<<a.n_chunks, 256, e_bytes, s>>>(a);
-  route_scan_kernel<<<1, 1024, e_bytes + 16, s>>>(a);
-  const int shared_blocks = r.has_shared ? dmoq_ceil_div(r.T, kChunk) : 0;
-  route_place_kernel<<<a.n_chunks + shared_blocks, 32, e_bytes, s>>>(a);
-  return dmoq_launch_status();
+  return launch_route(a, false, s);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -314,12 +391,7 @@ extern "C" int dmoq_route_build_static(const dmoq_route_t* route, const int64_t*
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t e_bytes = (size_t)r.E * sizeof(int32_t);
   if (a.n_chunks == 1 && (!r.has_shared || r.T <= 4 * kChunk)) {
-    route_fused_kernel<<<1, 1024, 2 * e_bytes + 16, s>>>(a);
-    return dmoq_launch_status();
+    return launch_route(a, true, s);
   }
-  route_hist_kernel<<<a.n_chunks, 256, e_bytes, s>>>(a);
-  route_scan_kernel<<<1, 1024, e_bytes + 16, s>>>(a);
-  const int shared_blocks = r.has_shared ? dmoq_ceil_div(r.T, kChunk) : 0;
-  route_place_kernel<<<a.n_chunks + shared_blocks, 32, e_bytes, s>>>(a);
-  return dmoq_launch_status();
+  return launch_route(a, false, s);
 }

@@ -595,36 +595,46 @@ class WxA16BitPartitionedGroupMoE(nn.Module):
             self._engine = eng
         return eng
 
-    def _run_graphed(self, eng, x, topk_w, topk_idx, shared_w):
+    def _body(self, eng, x, prof=None, partials=None):
+        """Router, shared-expert gate and the expert path for x (T, H)."""
+        gate_out = self.gate(x)
+        if isinstance(gate_out, tuple):
+            _, topk_w, topk_idx = gate_out
+        else:
+            topk_w, topk_idx = gate_out.softmax(dim=-1).topk(self.top_k, dim=-1)
+        shared_w = None
+        if eng.has_shared:
+            shared_w = torch.sigmoid(self.shared_expert_gate(x)).reshape(-1)
+        if prof is not None:
+            prof("router")
+        return eng.run(x, topk_w, topk_idx, shared_w, prof=prof, partials=partials)
+
+    def _run_graphed(self, eng, x):
         """First call for a token count runs eagerly (also finishes one-time kernel set-up); the second call
-        captures the whole expert path into a CUDA graph; later calls copy the inputs into the graph's static
-        buffers and replay it."""
+        captures router + expert path into a CUDA graph; later calls copy x into the graph's static input and
+        replay it.  The router must be capture-safe (no host synchronisation); set ``enable_cuda_graph = False``
+        for one that is not."""
         if self._graphs is None:
             self._graphs = {}
-        key = (x.shape[0], x.dtype, tuple(topk_idx.shape), shared_w is not None)
+        key = (x.shape[0], x.dtype)
         entry = self._graphs.get(key)
         if entry is None:
             self._graphs[key] = "warm"
-            return eng.run(x, topk_w, topk_idx, shared_w)
+            return self._body(eng, x)
         if entry == "warm":
             if len(self._graphs) > 8:
                 self._graphs = {key: "warm"}
-            st = dict(x=x.clone(), w=topk_w.to(torch.float32).clone(), i=topk_idx.to(torch.int64).clone(),
-                      s=None if shared_w is None else shared_w.to(torch.float32).clone())
+            static_x = x.clone()
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                st["y"] = eng.run(st["x"], st["w"], st["i"], st["s"])
-            entry = (graph, st)
+                static_y = self._body(eng, static_x)
+            entry = (graph, static_x, static_y)
             self._graphs[key] = entry
-        graph, st = entry
-        st["x"].copy_(x)
-        st["w"].copy_(topk_w)
-        st["i"].copy_(topk_idx)
-        if shared_w is not None:
-            st["s"].copy_(shared_w)
+        graph, static_x, static_y = entry
+        static_x.copy_(x)
         graph.replay()
-        return st["y"].clone()
+        return static_y.clone()
 
     def set_cuda_profile(self, enabled: bool = True):
         """CUDA-event stage timing into ``last_cuda_stats`` (adds one synchronise per forward)."""
@@ -654,21 +664,12 @@ class WxA16BitPartitionedGroupMoE(nn.Module):
         eng = self._get_engine(x.device)
         prof = _EventProfiler() if self.enable_cuda_profile else None
 
-        gate_out = self.gate(x)
-        if isinstance(gate_out, tuple):
-            _, topk_w, topk_idx = gate_out
+        graphed = (self.enable_cuda_graph and prof is None and _partials is None
+                   and x.shape[0] <= self.cuda_graph_max_tokens and not torch.cuda.is_current_stream_capturing())
+        if graphed:
+            y = self._run_graphed(eng, x)
         else:
-            topk_w, topk_idx = gate_out.softmax(dim=-1).topk(self.top_k, dim=-1)
-        shared_w = None
-        if eng.has_shared:
-            shared_w = torch.sigmoid(self.shared_expert_gate(x)).reshape(-1)
-        if prof is not None:
-            prof("router")
-        if (self.enable_cuda_graph and prof is None and _partials is None
-                and x.shape[0] <= self.cuda_graph_max_tokens and not torch.cuda.is_current_stream_capturing()):
-            y = self._run_graphed(eng, x, topk_w, topk_idx, shared_w)
-        else:
-            y = eng.run(x, topk_w, topk_idx, shared_w, prof=prof, partials=_partials)
+            y = self._body(eng, x, prof, _partials)
         if eng.shared_torch:
             y = y + self.shared_expert(x) * torch.sigmoid(self.shared_expert_gate(x))
         if prof is not None:

@@ -174,8 +174,8 @@ def test_rotate_quantize_vs_oracle_bit_exact(rows, dtype):
     q, s = K.rotate_quantize_fused_fp4_rowmajor(xd, rd, 128, 3)
     oq, os_ = O.actquant_e2m1(acc)
     assert np.array_equal(q.cpu().numpy(), oq) and np.array_equal(s.cpu().numpy(), os_)
-    r = K.batch_rotate_input(xd, 128, 46)
-    assert np.array_equal(r.cpu().numpy(), acc.astype(np.float16))
+    r = K.batch_rotate_input(xd, 128, 46)      # A16: a floating-point output, tensor-core accumulation order
+    assert rel_fro(r.float().cpu().numpy(), acc) < 1e-3
 
 
 def test_rotate_quantize_gather_and_errors():
