@@ -36,6 +36,15 @@ __device__ __forceinline__ void load_rotation(float* s_p, const uint16_t* rot_ma
   }
 }
 
+__device__ __forceinline__ float2 fma2_rn(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+
 __device__ __forceinline__ uint8_t e2m1_nibble(float y) {
   float a = fabsf(y);
   uint8_t mag = a < 0.25f ? 0 : a < 0.75f ? 1 : a < 1.25f ? 2 : a < 1.75f ? 3 : a < 2.5f ? 4 : a < 3.5f ? 5 : a < 5.0f ? 6 : 7;
@@ -79,13 +88,14 @@ __device__ void rotq_block(const RotArgs& a, const float* s_p, float* s_x, int g
   }
   __syncthreads();
 
-  // ---- 8x8 outputs per thread, sequential in k
+  // ---- 8x8 outputs per thread, sequential in k.  Two neighbouring columns share one packed FMA
+  // (fma.rn.f32x2: each half is an ordinary round-to-nearest fma, so every output is still its own chain).
   const int tx = tid % 16, ty = tid / 16;
-  float acc[8][8];
+  float2 acc2[8][4];
 #pragma unroll
   for (int r = 0; r < 8; ++r)
 #pragma unroll
-    for (int c = 0; c < 8; ++c) acc[r][c] = 0.f;
+    for (int c = 0; c < 4; ++c) acc2[r][c] = make_float2(0.f, 0.f);
 #pragma unroll 4
   for (int k = 0; k < kG; ++k) {
     const float4 x0 = *reinterpret_cast<const float4*>(&s_x[k * kXPitch + ty * 8]);
@@ -93,12 +103,22 @@ __device__ void rotq_block(const RotArgs& a, const float* s_p, float* s_x, int g
     const float4 p0 = *reinterpret_cast<const float4*>(&s_p[k * kPPitch + tx * 8]);
     const float4 p1 = *reinterpret_cast<const float4*>(&s_p[k * kPPitch + tx * 8 + 4]);
     const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-    const float pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+    const float2 pv[4] = {make_float2(p0.x, p0.y), make_float2(p0.z, p0.w), make_float2(p1.x, p1.y), make_float2(p1.z, p1.w)};
 #pragma unroll
-    for (int r = 0; r < 8; ++r)
+    for (int r = 0; r < 8; ++r) {
+      const float2 xx = make_float2(xv[r], xv[r]);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) acc[r][c] = fmaf(xv[r], pv[c], acc[r][c]);
+      for (int c = 0; c < 4; ++c) acc2[r][c] = fma2_rn(xx, pv[c], acc2[r][c]);
+    }
   }
+  float acc[8][8];
+#pragma unroll
+  for (int r = 0; r < 8; ++r)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      acc[r][2 * c] = acc2[r][c].x;
+      acc[r][2 * c + 1] = acc2[r][c].y;
+    }
   __syncthreads();  // s_x may be overwritten by the next block
 
   const int G = a.o_stride / kG;
@@ -237,12 +257,13 @@ int launch_tiles(const RotArgs& a, int tile_cap, cudaStream_t s) {
   return dmoq_launch_status();
 }
 
-// DMOQ_ROTQ=chain keeps every output on the CUDA-core FMA chain (A/B against the tensor-core kernel).
+// Quantised modes run the packed-FMA chain kernel; DMOQ_ROTQ=mma selects the tensor-core kernel with exact
+// fix-up instead (same codes).  The unquantised fp16 rotation always uses the tensor cores.
 bool use_mma_rotation() {
   static int cached = -1;
   if (cached < 0) {
     const char* v = getenv("DMOQ_ROTQ");
-    cached = (v && v[0] == 'c') ? 0 : 1;
+    cached = (v && v[0] == 'm') ? 1 : 0;
   }
   return cached == 1;
 }
@@ -284,7 +305,7 @@ extern "C" int dmoq_rotate_quant(int32_t mode, const void* x, int32_t src_is_bf1
   a.codes = codes;
   a.scales = scales;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (use_mma_rotation()) return dmoq_rotq_mma_rows(mode, a, s);
+  if (mode == DMOQ_A16 || use_mma_rotation()) return dmoq_rotq_mma_rows(mode, a, s);
   switch (mode) {
     case DMOQ_A16: return launch_rows<DMOQ_A16>(a, s);
     case DMOQ_A8: return launch_rows<DMOQ_A8>(a, s);
@@ -319,7 +340,7 @@ extern "C" int dmoq_rotate_quant_down(const dmoq_route_t* route, const dmoq_pool
   a.pool = pool_index;
   a.groups_per_member = p.inter / kG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (use_mma_rotation()) return dmoq_rotq_mma_tiles(p.mode, a, route->tile_cap, s);
+  if (p.mode == DMOQ_A16 || use_mma_rotation()) return dmoq_rotq_mma_tiles(p.mode, a, route->tile_cap, s);
   switch (p.mode) {
     case DMOQ_A16: return launch_tiles<DMOQ_A16>(a, route->tile_cap, s);
     case DMOQ_A8: return launch_tiles<DMOQ_A8>(a, route->tile_cap, s);

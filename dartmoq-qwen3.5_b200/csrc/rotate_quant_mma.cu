@@ -24,7 +24,8 @@ constexpr int kPitch32 = kG + 4;      // fp32 copies: padded rows, conflict-free
 constexpr size_t kOff_x16 = 0, kOff_p16 = 32768, kOff_x32 = 65536;
 constexpr size_t kOff_p32 = kOff_x32 + (size_t)kRows * kPitch32 * 4;
 constexpr size_t kOff_n2 = kOff_p32 + (size_t)kG * kPitch32 * 4;
-constexpr size_t kSmem = kOff_n2 + kRows * 4;
+constexpr size_t kOff_queue = kOff_n2 + kRows * 4;                 // 8 warps x 512 x (float result + u16 entry)
+constexpr size_t kSmem = kOff_queue + 8 * 512 * 6;
 
 __device__ __forceinline__ uint32_t swz256(int r, int c) { return (uint32_t)(r * 256 + ((c ^ (r & 7)) << 4)); }
 
@@ -76,21 +77,6 @@ __device__ __forceinline__ void stage_matrix(uint8_t* s16, float* s32, float* s_
   }
 }
 
-// the defining chain: acc = fma(x[k], p[k], acc), k = 0..127
-__device__ __forceinline__ float chain_dot(const float* xr, const float* pj) {
-  float acc = 0.f;
-#pragma unroll 8
-  for (int k = 0; k < kG; k += 4) {
-    const float4 xv = *reinterpret_cast<const float4*>(xr + k);
-    const float4 pv = *reinterpret_cast<const float4*>(pj + k);
-    acc = fmaf(xv.x, pv.x, acc);
-    acc = fmaf(xv.y, pv.y, acc);
-    acc = fmaf(xv.z, pv.z, acc);
-    acc = fmaf(xv.w, pv.w, acc);
-  }
-  return acc;
-}
-
 __device__ __forceinline__ uint32_t code_i8(float v) { return (uint32_t)(uint8_t)(int8_t)fminf(fmaxf(roundf(v), -127.f), 127.f); }
 __device__ __forceinline__ uint32_t code_e4m3(float v) { return (uint32_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3); }
 __device__ __forceinline__ uint32_t code_e2m1(float y) {
@@ -104,6 +90,73 @@ __device__ __forceinline__ float quad_max(float v) {
   return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
 }
 
+// ---- warp-cooperative exact values --------------------------------------------------------------
+// Few elements need their chain value, and which ones differs from lane to lane.  Letting each lane
+// compute its own would make the whole warp walk almost every element (divergence); instead the lanes
+// put (row, column) of their flagged elements into a per-warp queue, all 32 lanes then take queue
+// entries two at a time, and the owners read the results back.
+struct WarpQueue {
+  uint16_t* entry;   // kQueueCap x (row << 8 | col)
+  float* result;     // kQueueCap
+};
+constexpr int kQueueCap = 512;   // 32 lanes x 16 elements per pass
+
+// `mask`: flagged elements among this lane's v[i0 .. i0+16) (bit i = element i); row = tile row of the lane.
+__device__ __forceinline__ void resolve16(const WarpQueue& q, uint32_t mask, int i0, float (&v)[32], int row, int t4,
+                                          const float* x32, const float* p32) {
+  const int lane = threadIdx.x & 31;
+  const int cnt = __popc(mask);
+  int incl = cnt;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += n;
+  }
+  const int total = __shfl_sync(0xffffffffu, incl, 31);
+  if (total == 0) return;
+  const int off = incl - cnt;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const int i = i0 + j;
+    if ((mask >> i) & 1u) {
+      const int col = 8 * (i >> 1) + 2 * t4 + (i & 1);
+      q.entry[off + __popc(mask & ((1u << i) - 1u))] = (uint16_t)((row << 8) | col);
+    }
+  }
+  __syncwarp();
+  for (int base = 0; base < total; base += 64) {
+    const int e0 = base + lane, e1 = base + 32 + lane;
+    const int ent0 = q.entry[min(e0, total - 1)], ent1 = q.entry[min(e1, total - 1)];
+    const float* xa = x32 + (ent0 >> 8) * kPitch32;
+    const float* pa = p32 + (ent0 & 255) * kPitch32;
+    const float* xb = x32 + (ent1 >> 8) * kPitch32;
+    const float* pb = p32 + (ent1 & 255) * kPitch32;
+    float a0 = 0.f, a1 = 0.f;   // two independent chains per lane
+#pragma unroll 4
+    for (int k = 0; k < kG; k += 4) {
+      const float4 x0 = *reinterpret_cast<const float4*>(xa + k), p0 = *reinterpret_cast<const float4*>(pa + k);
+      const float4 x1 = *reinterpret_cast<const float4*>(xb + k), p1 = *reinterpret_cast<const float4*>(pb + k);
+      a0 = fmaf(x0.x, p0.x, a0);
+      a1 = fmaf(x1.x, p1.x, a1);
+      a0 = fmaf(x0.y, p0.y, a0);
+      a1 = fmaf(x1.y, p1.y, a1);
+      a0 = fmaf(x0.z, p0.z, a0);
+      a1 = fmaf(x1.z, p1.z, a1);
+      a0 = fmaf(x0.w, p0.w, a0);
+      a1 = fmaf(x1.w, p1.w, a1);
+    }
+    if (e0 < total) q.result[e0] = a0;
+    if (e1 < total) q.result[e1] = a1;
+  }
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const int i = i0 + j;
+    if ((mask >> i) & 1u) v[i] = q.result[off + __popc(mask & ((1u << i) - 1u))];
+  }
+  __syncwarp();
+}
+
 // One row block: rows [0, rows) of the staged x tile, group g.  `out_row(r)` = destination row.
 template <int MODE, typename OutRow>
 __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows, OutRow out_row) {
@@ -114,6 +167,9 @@ __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows,
   const float* n2 = reinterpret_cast<const float*>(smem + kOff_n2);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int mat = lane >> 3, rr = lane & 7, t4 = lane & 3;
+  WarpQueue wq;
+  wq.result = reinterpret_cast<float*>(smem + kOff_queue) + warp * kQueueCap;
+  wq.entry = reinterpret_cast<uint16_t*>(smem + kOff_queue + 8 * kQueueCap * 4) + warp * kQueueCap;
 
   // ---- approximate rotation on the tensor cores: warp = 16 rows x 128 columns
   float acc[16][4];
@@ -140,8 +196,6 @@ __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows,
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = warp * 16 + (lane >> 2) + h * 8;
-    const float* xr = x32 + r * kPitch32;
-    auto col = [&](int i) { return 8 * (i >> 1) + 2 * t4 + (i & 1); };
     float v[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = acc[i >> 1][h * 2 + (i & 1)];
@@ -154,7 +208,8 @@ __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows,
       continue;
     }
     const float delta = ldexpf(sqrtf(n2[r]), -16) * 1.01f;
-    const bool live = r < rows;   // padding rows take part in the warp shuffles but get no fix-up work
+    // padding rows and all-zero rows take part in the warp-wide steps but never ask for a chain value
+    const bool live = r < rows && n2[r] > 0.f;
 
     if (MODE == DMOQ_A8 || MODE == DMOQ_FP8) {
       float m = 0.f;
@@ -163,38 +218,47 @@ __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows,
       m = quad_max(m);
       const float thr = live ? m - 2.f * delta : 3.0e38f;
       uint32_t exact = 0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) exact |= (fabsf(v[i]) >= thr) ? (1u << i) : 0u;
+      resolve16(wq, exact & 0xFFFFu, 0, v, r, t4, x32, p32);
+      resolve16(wq, exact & 0xFFFF0000u, 16, v, r, t4, x32, p32);
       float cm = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        if (fabsf(v[i]) >= thr) {
-          v[i] = chain_dot(xr, p32 + col(i) * kPitch32);
-          exact |= 1u << i;
-          cm = fmaxf(cm, fabsf(v[i]));
-        }
-      }
+      for (int i = 0; i < 32; ++i) cm = ((exact >> i) & 1u) ? fmaxf(cm, fabsf(v[i])) : cm;
       const float amax = quad_max(cm);
       const float full = (MODE == DMOQ_A8) ? 127.0f : 448.0f;
       const float tiny = (MODE == DMOQ_A8) ? (float)(1e-8 * 127.0) : (float)(1e-8 * 448.0);
       const float s = (amax < tiny) ? 1e-8f : __fdiv_rn(amax, full);
-      const float t = delta / s * 1.001f + 2e-5f;
+      const float inv_s = 1.0f / s;
+      const float t = delta * inv_s * 1.001f + 3e-5f;   // also covers v*inv_s versus the IEEE quotient v/s
+      uint32_t amb = 0;
+      if (live) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float q0 = v[i] * inv_s, q1 = v[i + 1] * inv_s;
+          if (MODE == DMOQ_A8) {
+            amb |= (fabsf(q0 - rintf(q0)) > 0.5f - t) ? (1u << i) : 0u;
+            amb |= (fabsf(q1 - rintf(q1)) > 0.5f - t) ? (2u << i) : 0u;
+          } else {
+            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0 - t, q1 - t), __NV_SATFINITE, __NV_E4M3);
+            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q0 + t, q1 + t), __NV_SATFINITE, __NV_E4M3);
+            const uint32_t d = lo ^ hi;
+            amb |= (d & 0xFFu) ? (1u << i) : 0u;
+            amb |= (d & 0xFF00u) ? (2u << i) : 0u;
+          }
+        }
+        amb &= ~exact;
+      }
+      resolve16(wq, amb & 0xFFFFu, 0, v, r, t4, x32, p32);
+      resolve16(wq, amb & 0xFFFF0000u, 16, v, r, t4, x32, p32);
+      exact |= amb;
       uint32_t c[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        if (!live) {
-          c[i] = 0;
-          continue;
-        }
-        float q = __fdiv_rn(v[i], s);
-        if (!((exact >> i) & 1u)) {
-          const uint32_t lo = (MODE == DMOQ_A8) ? code_i8(q - t) : code_e4m3(q - t);
-          const uint32_t hi = (MODE == DMOQ_A8) ? code_i8(q + t) : code_e4m3(q + t);
-          if (lo == hi) {
-            c[i] = lo;
-            continue;
-          }
-          q = __fdiv_rn(chain_dot(xr, p32 + col(i) * kPitch32), s);
-        }
-        c[i] = (MODE == DMOQ_A8) ? code_i8(q) : code_e4m3(q);
+        // chain values go through the IEEE quotient exactly as the definition does; for the others the
+        // test above guarantees that the approximate quotient rounds to the same code
+        const float q = ((exact >> i) & 1u) ? __fdiv_rn(v[i], s) : v[i] * inv_s;
+        c[i] = live ? ((MODE == DMOQ_A8) ? code_i8(q) : code_e4m3(q)) : 0u;
       }
 #pragma unroll
       for (int nt = 0; nt < 16; ++nt)
@@ -202,52 +266,51 @@ __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows,
       if (t4 == 0 && r < rows)
         reinterpret_cast<__half*>(a.scales)[(size_t)out_row(r) * (a.o_stride / kG) + g] = __float2half_rn(__fmul_rn(s, a.extra_scale));
     } else {  // FP4: four 32-column blocks per row, 8 values of each block per thread
-      uint32_t e_bytes = 0;
+      float mb[4], thr[4];
+      uint32_t exact = 0;
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
         float m = 0.f;
 #pragma unroll
         for (int i = 8 * b; i < 8 * b + 8; ++i) m = fmaxf(m, fabsf(v[i]));
-        m = quad_max(m);
-        const float thr = live ? m - 2.f * delta : 3.0e38f;
-        uint32_t exact = 0;
+        mb[b] = quad_max(m);
+        thr[b] = live ? mb[b] - 2.f * delta : 3.0e38f;
+#pragma unroll
+        for (int i = 8 * b; i < 8 * b + 8; ++i) exact |= (fabsf(v[i]) >= thr[b]) ? (1u << i) : 0u;
+      }
+      resolve16(wq, exact & 0xFFFFu, 0, v, r, t4, x32, p32);
+      resolve16(wq, exact & 0xFFFF0000u, 16, v, r, t4, x32, p32);
+      uint32_t e_bytes = 0, amb = 0;
+      int ei[4];
+      float tb[4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
         float cm = 0.f;
 #pragma unroll
-        for (int i = 8 * b; i < 8 * b + 8; ++i) {
-          if (fabsf(v[i]) >= thr) {
-            v[i] = chain_dot(xr, p32 + col(i) * kPitch32);
-            exact |= 1u << i;
-            cm = fmaxf(cm, fabsf(v[i]));
-          }
-        }
+        for (int i = 8 * b; i < 8 * b + 8; ++i) cm = ((exact >> i) & 1u) ? fmaxf(cm, fabsf(v[i])) : cm;
         const float amax = fmaxf(quad_max(cm), 1e-30f);
         float e = ceilf((float)log2((double)__fdiv_rn(amax, 6.0f)));
         e = fminf(fmaxf(e, -127.f), 127.f);
-        const int ei = (int)e;
-        e_bytes |= (uint32_t)(ei + 127) << (8 * b);
-        const float t = ldexpf(delta, -ei) * 1.001f + 1e-6f;
+        ei[b] = (int)e;
+        e_bytes |= (uint32_t)(ei[b] + 127) << (8 * b);
+        tb[b] = ldexpf(delta, -ei[b]) * 1.001f + 1e-6f;
+        if (live) {
 #pragma unroll
-        for (int i = 8 * b; i < 8 * b + 8; i += 2) {
-          uint32_t nib[2];
-#pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            if (!live) {
-              nib[q] = 0;
-              continue;
-            }
-            float y = ldexpf(v[i + q], -ei);
-            if (!((exact >> (i + q)) & 1u)) {
-              const uint32_t lo = code_e2m1(y - t), hi = code_e2m1(y + t);
-              if (lo == hi) {
-                nib[q] = lo;
-                continue;
-              }
-              y = ldexpf(chain_dot(xr, p32 + col(i + q) * kPitch32), -ei);
-            }
-            nib[q] = code_e2m1(y);
+          for (int i = 8 * b; i < 8 * b + 8; ++i) {
+            const float y = ldexpf(v[i], -ei[b]);
+            amb |= (code_e2m1(y - tb[b]) != code_e2m1(y + tb[b])) ? (1u << i) : 0u;
           }
-          srow[(8 * (i >> 1) + 2 * t4) >> 1] = (uint8_t)(nib[0] | (nib[1] << 4));
         }
+      }
+      amb &= ~exact;
+      resolve16(wq, amb & 0xFFFFu, 0, v, r, t4, x32, p32);
+      resolve16(wq, amb & 0xFFFF0000u, 16, v, r, t4, x32, p32);
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const int b = i >> 3;
+        const uint32_t n0 = live ? code_e2m1(ldexpf(v[i], -ei[b])) : 0u;
+        const uint32_t n1 = live ? code_e2m1(ldexpf(v[i + 1], -ei[b])) : 0u;
+        srow[(8 * (i >> 1) + 2 * t4) >> 1] = (uint8_t)(n0 | (n1 << 4));
       }
       if (t4 == 0 && r < rows)
         *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.scales) + (size_t)out_row(r) * (a.o_stride / 32) + g * 4) = e_bytes;
