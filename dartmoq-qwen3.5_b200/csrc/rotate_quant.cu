@@ -257,13 +257,13 @@ int launch_tiles(const RotArgs& a, int tile_cap, cudaStream_t s) {
   return dmoq_launch_status();
 }
 
-// Quantised modes run the packed-FMA chain kernel; DMOQ_ROTQ=mma selects the tensor-core kernel with exact
-// fix-up instead (same codes).  The unquantised fp16 rotation always uses the tensor cores.
+// The tensor-core kernel with exact fix-up is the default; DMOQ_ROTQ=chain computes every value on the CUDA-core
+// FMA chain instead (same codes, for A/B runs).  The unquantised fp16 rotation always uses the tensor cores.
 bool use_mma_rotation() {
   static int cached = -1;
   if (cached < 0) {
     const char* v = getenv("DMOQ_ROTQ");
-    cached = (v && v[0] == 'm') ? 1 : 0;
+    cached = (v && v[0] == 'c') ? 0 : 1;
   }
   return cached == 1;
 }

@@ -2,7 +2,7 @@
 //
 // The codes are DEFINED through a sequential fp32 FMA chain over k = 0..127 per rotated value (that is
 // what a CPU can reproduce bit for bit).  Computing every value that way costs 128 dependent FMAs; this
-// kernel gets the same codes ~5x cheaper:
+// kernel gets the same codes with a few percent of that work:
 //   1. all 128x128 rotated values of a row block come from fp16 tensor-core MMAs (fp32 accumulate);
 //      they differ from the chain values by at most delta = 2^-16 * |x_row|_2  (the chain's own worst-case
 //      rounding bound is 127 * 2^-24 * |x|_2 |p|_2 < 2^-17 |x|_2; the same again is allowed for the MMA);
@@ -10,6 +10,8 @@
 //      approximate maximum, so the scale is the exact one;
 //   3. an element keeps the code of its approximate value only if the whole interval [v-t, v+t]
 //      (t = delta / scale) quantises to ONE code; otherwise its chain value is computed and quantised.
+// The elements of steps 2 and 3 (about 1 % and 2 % of a block) go through a block-wide queue, so that the
+// 256 threads share the chains evenly whichever lanes flagged them.
 // Quantisation rules: turboquant_utils/triton_kernels_a8.py:473-484 (int8), triton_kernels_fp8.py:176-187
 // (e4m3), triton_kernels_fp4.py:1073-1104 (e2m1 + per-32 e8m0).  The unquantised fp16 output (A16 mode,
 // rotation.py:176) is the rounded MMA value: a floating-point output, not a code.
@@ -20,12 +22,16 @@ namespace {
 constexpr int kG = DMOQ_GROUP;
 constexpr int kRows = 128;            // rows per block
 constexpr int kThreads = 256;         // 8 warps x 16 rows
-constexpr int kPitch32 = kG + 4;      // fp32 copies: padded rows, conflict-free 16-byte reads across rows
-constexpr size_t kOff_x16 = 0, kOff_p16 = 32768, kOff_x32 = 65536;
-constexpr size_t kOff_p32 = kOff_x32 + (size_t)kRows * kPitch32 * 4;
-constexpr size_t kOff_n2 = kOff_p32 + (size_t)kG * kPitch32 * 4;
-constexpr size_t kOff_queue = kOff_n2 + kRows * 4;                 // 8 warps x 512 x (float result + u16 entry)
-constexpr size_t kSmem = kOff_queue + 8 * 512 * 6;
+constexpr int kPitchQ = 144;          // staged code row: 128 one-byte codes + pad (conflict-free 2-byte stores)
+constexpr int kPitchH = 272;          // staged fp16 row (A16)
+constexpr int kQueueCap = 2048;
+constexpr size_t kOff_x16 = 0, kOff_p16 = 32768, kOff_stage = 65536;
+constexpr size_t kOff_n2 = kOff_stage + (size_t)kRows * kPitchH;   // |x_row|^2
+constexpr size_t kOff_rowmax = kOff_n2 + kRows * 4;                // u32 bits of the exact max |v| per (row, 32-col block)
+constexpr size_t kOff_tab = kOff_rowmax + kRows * 16;              // scale (float) or exponent (int) per (row, block)
+constexpr size_t kOff_wsum = kOff_tab + kRows * 16;                // per-warp queue counts, one set per phase
+constexpr size_t kOff_queue = kOff_wsum + 64;
+constexpr size_t kSmem = kOff_queue + (size_t)kQueueCap * 2;       // ~107 KB: two blocks per SM
 
 __device__ __forceinline__ uint32_t swz256(int r, int c) { return (uint32_t)(r * 256 + ((c ^ (r & 7)) << 4)); }
 
@@ -40,40 +46,40 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], u
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// 128 x 128 fp16 matrix (row pitch `pitch` elements in global memory) -> swizzled fp16 tile + padded fp32 copy.
-// Thread t stages 64 columns of row t/2.  `row_src(r)` gives the global row or -1 (zero row).
+// 128 x 128 fp16 matrix (row pitch `pitch` elements in global memory) -> swizzled fp16 tile.  Sixteen
+// consecutive lanes read the 256 bytes of one row.  `row_src(r)` gives the global row or -1 (zero row).
 template <typename RowSrc>
-__device__ __forceinline__ void stage_matrix(uint8_t* s16, float* s32, float* s_n2, const void* base, int is_bf16,
-                                             size_t pitch, size_t col0, RowSrc row_src) {
-  const int r = threadIdx.x >> 1, hh = threadIdx.x & 1;
-  const long long src = row_src(r);
-  float ss = 0.f;
+__device__ __forceinline__ void stage_matrix(uint8_t* s16, float* s_n2, const void* base, int is_bf16, size_t pitch,
+                                             size_t col0, RowSrc row_src) {
+  const int c = threadIdx.x & 15;
+  uint4 raw[8];
+  bool have[8];
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {
+  for (int j = 0; j < 8; ++j) {
+    const int r = (threadIdx.x >> 4) + 16 * j;
+    const long long src = row_src(r);
+    have[j] = src >= 0;
+    raw[j] = make_uint4(0u, 0u, 0u, 0u);
+    if (have[j]) raw[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + (size_t)src * pitch + col0 + c * 8);
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int r = (threadIdx.x >> 4) + 16 * j;
     __align__(16) __half h[8];
-    if (src >= 0) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + (size_t)src * pitch + col0 + hh * 64 + c * 8);
-      const uint16_t* u = reinterpret_cast<const uint16_t*>(&raw);
-#pragma unroll
-      for (int q = 0; q < 8; ++q) h[q] = is_bf16 ? __float2half_rn(bf16_bits_to_float(u[q])) : __ushort_as_half(u[q]);
-    } else {
-#pragma unroll
-      for (int q = 0; q < 8; ++q) h[q] = __ushort_as_half((uint16_t)0);
-    }
-    *reinterpret_cast<uint4*>(s16 + swz256(r, hh * 8 + c)) = *reinterpret_cast<const uint4*>(h);
-    float f[8];
+    const uint16_t* u = reinterpret_cast<const uint16_t*>(&raw[j]);
+    float ss = 0.f;
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
-      f[q] = __half2float(h[q]);
-      ss = fmaf(f[q], f[q], ss);
+      h[q] = is_bf16 ? __float2half_rn(bf16_bits_to_float(u[q])) : __ushort_as_half(u[q]);
+      const float f = __half2float(h[q]);
+      ss = fmaf(f, f, ss);
     }
-    float* dst = s32 + r * kPitch32 + hh * 64 + c * 8;
-    *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
-    *reinterpret_cast<float4*>(dst + 4) = make_float4(f[4], f[5], f[6], f[7]);
-  }
-  if (s_n2 != nullptr) {
-    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-    if (hh == 0) s_n2[r] = ss;
+    *reinterpret_cast<uint4*>(s16 + swz256(r, c)) = *reinterpret_cast<const uint4*>(h);
+    if (s_n2 != nullptr) {
+#pragma unroll
+      for (int d = 1; d < 16; d <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+      if (c == 0) s_n2[r] = ss;
+    }
   }
 }
 
@@ -90,86 +96,131 @@ __device__ __forceinline__ float quad_max(float v) {
   return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
 }
 
-// ---- warp-cooperative exact values --------------------------------------------------------------
-// Few elements need their chain value, and which ones differs from lane to lane.  Letting each lane
-// compute its own would make the whole warp walk almost every element (divergence); instead the lanes
-// put (row, column) of their flagged elements into a per-warp queue, all 32 lanes then take queue
-// entries two at a time, and the owners read the results back.
-struct WarpQueue {
-  uint16_t* entry;   // kQueueCap x (row << 8 | col)
-  float* result;     // kQueueCap
+// ---- exact values: sequential fp32 chains read from the fp16 tiles --------------------------------
+struct ChainSrc {
+  const uint8_t* row;
+  uint32_t sw;
 };
-constexpr int kQueueCap = 512;   // 32 lanes x 16 elements per pass
+__device__ __forceinline__ ChainSrc chain_src(const uint8_t* tile, int r) { return ChainSrc{tile + r * 256, (uint32_t)(r & 7) << 4}; }
 
-// `mask`: flagged elements among this lane's v[i0 .. i0+16) (bit i = element i); row = tile row of the lane.
-__device__ __forceinline__ void resolve16(const WarpQueue& q, uint32_t mask, int i0, float (&v)[32], int row, int t4,
-                                          const float* x32, const float* p32) {
-  const int lane = threadIdx.x & 31;
-  const int cnt = __popc(mask);
+__device__ __forceinline__ void chain_step(float& acc, const uint4& xv, const uint4& pv) {
+  const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+  const __half2* ph = reinterpret_cast<const __half2*>(&pv);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float2 xf = __half22float2(xh[q]), pf = __half22float2(ph[q]);
+    acc = fmaf(xf.x, pf.x, acc);
+    acc = fmaf(xf.y, pf.y, acc);
+  }
+}
+__device__ __forceinline__ float chain1(ChainSrc x, ChainSrc p) {
+  float acc = 0.f;
+#pragma unroll 4
+  for (uint32_t c = 0; c < 256; c += 16)
+    chain_step(acc, *reinterpret_cast<const uint4*>(x.row + (c ^ x.sw)), *reinterpret_cast<const uint4*>(p.row + (c ^ p.sw)));
+  return acc;
+}
+__device__ __forceinline__ void chain2(ChainSrc x0, ChainSrc p0, ChainSrc x1, ChainSrc p1, float& r0, float& r1) {
+  float a0 = 0.f, a1 = 0.f;
+#pragma unroll 2
+  for (uint32_t c = 0; c < 256; c += 16) {
+    const uint4 xa = *reinterpret_cast<const uint4*>(x0.row + (c ^ x0.sw)), pa = *reinterpret_cast<const uint4*>(p0.row + (c ^ p0.sw));
+    const uint4 xb = *reinterpret_cast<const uint4*>(x1.row + (c ^ x1.sw)), pb = *reinterpret_cast<const uint4*>(p1.row + (c ^ p1.sw));
+    chain_step(a0, xa, pa);
+    chain_step(a1, xb, pb);
+  }
+  r0 = a0;
+  r1 = a1;
+}
+
+// What a thread does with the chain value of queue entry (row, col).
+//   PHASE 1: fold |v| into the exact maximum of the entry's (row, 32-column block).
+//   PHASE 2: quantise with the row's / block's scale and overwrite the staged approximate code.
+template <int MODE, int PHASE>
+__device__ __forceinline__ void consume(uint8_t* smem, int ent, float v) {
+  const int row = ent >> 8, col = ent & 255;
+  const int blk = (MODE == DMOQ_FP4) ? (col >> 5) : 0;
+  if (PHASE == 1) {
+    atomicMax(reinterpret_cast<uint32_t*>(smem + kOff_rowmax) + row * 4 + blk, __float_as_uint(fabsf(v)));
+  } else {
+    uint32_t code;
+    if (MODE == DMOQ_FP4) {
+      code = code_e2m1(ldexpf(v, -reinterpret_cast<const int*>(smem + kOff_tab)[row * 4 + blk]));
+    } else {
+      const float q = __fdiv_rn(v, reinterpret_cast<const float*>(smem + kOff_tab)[row * 4]);
+      code = (MODE == DMOQ_A8) ? code_i8(q) : code_e4m3(q);
+    }
+    smem[kOff_stage + row * kPitchQ + col] = (uint8_t)code;
+  }
+}
+
+// Block-wide queue.  mask[h] flags elements of this thread's row (rbase + 8h): bit i = the thread's i-th value of
+// that row, column 8*(i/2) + 2*t4 + (i&1).  Every thread of the block must call this (it synchronises).
+template <int MODE, int PHASE>
+__device__ __forceinline__ void resolve(uint8_t* smem, const uint32_t (&mask)[2], int rbase, int t4) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int* wsum = reinterpret_cast<int*>(smem + kOff_wsum) + (PHASE - 1) * 8;
+  uint16_t* entry = reinterpret_cast<uint16_t*>(smem + kOff_queue);
+  const int cnt = __popc(mask[0]) + __popc(mask[1]);
   int incl = cnt;
 #pragma unroll
   for (int d = 1; d < 32; d <<= 1) {
     const int n = __shfl_up_sync(0xffffffffu, incl, d);
     if (lane >= d) incl += n;
   }
-  const int total = __shfl_sync(0xffffffffu, incl, 31);
-  if (total == 0) return;
-  const int off = incl - cnt;
+  if (lane == 31) wsum[warp] = incl;
+  __syncthreads();
+  int first = incl - cnt, total = 0;
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    const int i = i0 + j;
-    if ((mask >> i) & 1u) {
-      const int col = 8 * (i >> 1) + 2 * t4 + (i & 1);
-      q.entry[off + __popc(mask & ((1u << i) - 1u))] = (uint16_t)((row << 8) | col);
-    }
+  for (int w = 0; w < 8; ++w) {
+    const int n = wsum[w];
+    total += n;
+    if (w < warp) first += n;
   }
-  __syncwarp();
-  for (int base = 0; base < total; base += 64) {
-    const int e0 = base + lane, e1 = base + 32 + lane;
-    const int ent0 = q.entry[min(e0, total - 1)], ent1 = q.entry[min(e1, total - 1)];
-    const float* xa = x32 + (ent0 >> 8) * kPitch32;
-    const float* pa = p32 + (ent0 & 255) * kPitch32;
-    const float* xb = x32 + (ent1 >> 8) * kPitch32;
-    const float* pb = p32 + (ent1 & 255) * kPitch32;
-    float a0 = 0.f, a1 = 0.f;   // two independent chains per lane
-#pragma unroll 4
-    for (int k = 0; k < kG; k += 4) {
-      const float4 x0 = *reinterpret_cast<const float4*>(xa + k), p0 = *reinterpret_cast<const float4*>(pa + k);
-      const float4 x1 = *reinterpret_cast<const float4*>(xb + k), p1 = *reinterpret_cast<const float4*>(pb + k);
-      a0 = fmaf(x0.x, p0.x, a0);
-      a1 = fmaf(x1.x, p1.x, a1);
-      a0 = fmaf(x0.y, p0.y, a0);
-      a1 = fmaf(x1.y, p1.y, a1);
-      a0 = fmaf(x0.z, p0.z, a0);
-      a1 = fmaf(x1.z, p1.z, a1);
-      a0 = fmaf(x0.w, p0.w, a0);
-      a1 = fmaf(x1.w, p1.w, a1);
-    }
-    if (e0 < total) q.result[e0] = a0;
-    if (e1 < total) q.result[e1] = a1;
-  }
-  __syncwarp();
+  const uint8_t* x16 = smem + kOff_x16;
+  const uint8_t* p16 = smem + kOff_p16;
+  for (int q0 = 0; q0 < total; q0 += kQueueCap) {   // one round unless more than kQueueCap elements are flagged
+    int rank = first - q0;
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    const int i = i0 + j;
-    if ((mask >> i) & 1u) v[i] = q.result[off + __popc(mask & ((1u << i) - 1u))];
+    for (int h = 0; h < 2; ++h) {
+      uint32_t m = mask[h];
+      while (m) {
+        const int i = __ffs(m) - 1;
+        m &= m - 1;
+        if ((unsigned)rank < (unsigned)kQueueCap)
+          entry[rank] = (uint16_t)(((rbase + 8 * h) << 8) | (8 * (i >> 1) + 2 * t4 + (i & 1)));
+        ++rank;
+      }
+    }
+    __syncthreads();
+    const int n = min(kQueueCap, total - q0);
+    for (int i = tid; i < n; i += 2 * kThreads) {
+      const int e0 = entry[i];
+      if (i + kThreads < n) {
+        const int e1 = entry[i + kThreads];
+        float v0, v1;
+        chain2(chain_src(x16, e0 >> 8), chain_src(p16, e0 & 255), chain_src(x16, e1 >> 8), chain_src(p16, e1 & 255), v0, v1);
+        consume<MODE, PHASE>(smem, e0, v0);
+        consume<MODE, PHASE>(smem, e1, v1);
+      } else {
+        consume<MODE, PHASE>(smem, e0, chain1(chain_src(x16, e0 >> 8), chain_src(p16, e0 & 255)));
+      }
+    }
+    if (q0 + kQueueCap < total) __syncthreads();   // the queue is refilled
   }
-  __syncwarp();
+  __syncthreads();
 }
 
 // One row block: rows [0, rows) of the staged x tile, group g.  `out_row(r)` = destination row.
 template <int MODE, typename OutRow>
 __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows, OutRow out_row) {
-  uint8_t* x16 = smem + kOff_x16;
+  const uint8_t* x16 = smem + kOff_x16;
   const uint8_t* p16 = smem + kOff_p16;
-  const float* x32 = reinterpret_cast<const float*>(smem + kOff_x32);
-  const float* p32 = reinterpret_cast<const float*>(smem + kOff_p32);
+  uint8_t* stage = smem + kOff_stage;
   const float* n2 = reinterpret_cast<const float*>(smem + kOff_n2);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int mat = lane >> 3, rr = lane & 7, t4 = lane & 3;
-  WarpQueue wq;
-  wq.result = reinterpret_cast<float*>(smem + kOff_queue) + warp * kQueueCap;
-  wq.entry = reinterpret_cast<uint16_t*>(smem + kOff_queue + 8 * kQueueCap * 4) + warp * kQueueCap;
+  const int rbase = warp * 16 + (lane >> 2);
 
   // ---- approximate rotation on the tensor cores: warp = 16 rows x 128 columns
   float acc[16][4];
@@ -190,152 +241,162 @@ __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows,
       mma_f16(acc[2 * np + 1], af, bf[2], bf[3]);
     }
   }
-  __syncthreads();  // every warp is done reading x16: it becomes the output staging tile
 
-  constexpr int ROWB = (MODE == DMOQ_A16) ? 256 : (MODE == DMOQ_FP4) ? 64 : 128;  // staged bytes per row
+  if (MODE == DMOQ_A16) {
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int r = warp * 16 + (lane >> 2) + h * 8;
-    float v[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = acc[i >> 1][h * 2 + (i & 1)];
-    uint8_t* srow = x16 + r * ROWB;
-
-    if (MODE == DMOQ_A16) {
+    for (int h = 0; h < 2; ++h)
 #pragma unroll
       for (int nt = 0; nt < 16; ++nt)
-        *reinterpret_cast<__half2*>(srow + (8 * nt + 2 * t4) * 2) = __floats2half2_rn(v[2 * nt], v[2 * nt + 1]);
-      continue;
+        *reinterpret_cast<__half2*>(stage + (rbase + 8 * h) * kPitchH + (8 * nt + 2 * t4) * 2) =
+            __floats2half2_rn(acc[nt][2 * h], acc[nt][2 * h + 1]);
+    __syncthreads();
+  } else {
+    constexpr int NB = (MODE == DMOQ_FP4) ? 4 : 1;      // scale blocks per row of the group
+    constexpr int TPB = 16 / NB;                         // n-tiles (8 columns each) per scale block
+    float delta[2];
+    bool live[2];
+    uint32_t mask[2];
+    // ---- phase 1: the exact maximum of every row / block
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = rbase + 8 * h;
+      const float nn = n2[r];
+      delta[h] = ldexpf(sqrtf(nn), -16) * 1.01f;
+      live[h] = r < rows && nn > 0.f;   // padding rows and all-zero rows never ask for a chain value
+      mask[h] = 0;
+#pragma unroll
+      for (int b = 0; b < NB; ++b) {
+        float m = 0.f;
+#pragma unroll
+        for (int nt = b * TPB; nt < (b + 1) * TPB; ++nt) m = fmaxf(m, fmaxf(fabsf(acc[nt][2 * h]), fabsf(acc[nt][2 * h + 1])));
+        m = quad_max(m);
+        const float thr = live[h] ? m - 2.f * delta[h] : 3.0e38f;
+#pragma unroll
+        for (int nt = b * TPB; nt < (b + 1) * TPB; ++nt) {
+          mask[h] |= (fabsf(acc[nt][2 * h]) >= thr) ? (1u << (2 * nt)) : 0u;
+          mask[h] |= (fabsf(acc[nt][2 * h + 1]) >= thr) ? (2u << (2 * nt)) : 0u;
+        }
+      }
     }
-    const float delta = ldexpf(sqrtf(n2[r]), -16) * 1.01f;
-    // padding rows and all-zero rows take part in the warp-wide steps but never ask for a chain value
-    const bool live = r < rows && n2[r] > 0.f;
+    resolve<MODE, 1>(smem, mask, rbase, t4);
 
-    if (MODE == DMOQ_A8 || MODE == DMOQ_FP8) {
-      float m = 0.f;
+    // ---- phase 2: approximate codes for everything, exact ones where the approximation cannot decide
+    const uint32_t* rowmax = reinterpret_cast<const uint32_t*>(smem + kOff_rowmax);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) m = fmaxf(m, fabsf(v[i]));
-      m = quad_max(m);
-      const float thr = live ? m - 2.f * delta : 3.0e38f;
-      uint32_t exact = 0;
+    for (int h = 0; h < 2; ++h) {
+      const int r = rbase + 8 * h;
+      uint8_t* srow = stage + r * kPitchQ;
+      mask[h] = 0;
+      if (MODE == DMOQ_A8 || MODE == DMOQ_FP8) {
+        const float amax = __uint_as_float(rowmax[r * 4]);
+        const float full = (MODE == DMOQ_A8) ? 127.0f : 448.0f;
+        const float tiny = (MODE == DMOQ_A8) ? (float)(1e-8 * 127.0) : (float)(1e-8 * 448.0);
+        const float s = (amax < tiny) ? 1e-8f : __fdiv_rn(amax, full);
+        const float inv_s = 1.0f / s;
+        const float t = delta[h] * inv_s * 1.001f + 3e-5f;   // also covers v*inv_s versus the IEEE quotient v/s
+        if (t4 == 0) {
+          reinterpret_cast<float*>(smem + kOff_tab)[r * 4] = s;
+          if (r < rows)
+            reinterpret_cast<__half*>(a.scales)[(size_t)out_row(r) * (a.o_stride / kG) + g] = __float2half_rn(__fmul_rn(s, a.extra_scale));
+        }
 #pragma unroll
-      for (int i = 0; i < 32; ++i) exact |= (fabsf(v[i]) >= thr) ? (1u << i) : 0u;
-      resolve16(wq, exact & 0xFFFFu, 0, v, r, t4, x32, p32);
-      resolve16(wq, exact & 0xFFFF0000u, 16, v, r, t4, x32, p32);
-      float cm = 0.f;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) cm = ((exact >> i) & 1u) ? fmaxf(cm, fabsf(v[i])) : cm;
-      const float amax = quad_max(cm);
-      const float full = (MODE == DMOQ_A8) ? 127.0f : 448.0f;
-      const float tiny = (MODE == DMOQ_A8) ? (float)(1e-8 * 127.0) : (float)(1e-8 * 448.0);
-      const float s = (amax < tiny) ? 1e-8f : __fdiv_rn(amax, full);
-      const float inv_s = 1.0f / s;
-      const float t = delta * inv_s * 1.001f + 3e-5f;   // also covers v*inv_s versus the IEEE quotient v/s
-      uint32_t amb = 0;
-      if (live) {
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float q0 = v[i] * inv_s, q1 = v[i + 1] * inv_s;
+        for (int nt = 0; nt < 16; ++nt) {
+          const float q0 = acc[nt][2 * h] * inv_s, q1 = acc[nt][2 * h + 1] * inv_s;
+          uint32_t c01;
           if (MODE == DMOQ_A8) {
-            amb |= (fabsf(q0 - rintf(q0)) > 0.5f - t) ? (1u << i) : 0u;
-            amb |= (fabsf(q1 - rintf(q1)) > 0.5f - t) ? (2u << i) : 0u;
+            const float r0 = rintf(q0), r1 = rintf(q1);
+            mask[h] |= (fabsf(q0 - r0) > 0.5f - t) ? (1u << (2 * nt)) : 0u;
+            mask[h] |= (fabsf(q1 - r1) > 0.5f - t) ? (2u << (2 * nt)) : 0u;
+            c01 = code_i8(q0) | (code_i8(q1) << 8);
           } else {
             const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0 - t, q1 - t), __NV_SATFINITE, __NV_E4M3);
             const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q0 + t, q1 + t), __NV_SATFINITE, __NV_E4M3);
             const uint32_t d = lo ^ hi;
-            amb |= (d & 0xFFu) ? (1u << i) : 0u;
-            amb |= (d & 0xFF00u) ? (2u << i) : 0u;
+            mask[h] |= (d & 0xFFu) ? (1u << (2 * nt)) : 0u;
+            mask[h] |= (d & 0xFF00u) ? (2u << (2 * nt)) : 0u;
+            c01 = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
+          }
+          *reinterpret_cast<uint16_t*>(srow + 8 * nt + 2 * t4) = live[h] ? (uint16_t)c01 : (uint16_t)0;
+        }
+      } else {
+        uint32_t e_bytes = 0;
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+          const float amax = fmaxf(__uint_as_float(rowmax[r * 4 + b]), 1e-30f);
+          float e = ceilf((float)log2((double)__fdiv_rn(amax, 6.0f)));
+          e = fminf(fmaxf(e, -127.f), 127.f);
+          const int ei = (int)e;
+          e_bytes |= (uint32_t)(ei + 127) << (8 * b);
+          if (t4 == 0) reinterpret_cast<int*>(smem + kOff_tab)[r * 4 + b] = ei;
+          const float tb = ldexpf(delta[h], -ei) * 1.001f + 1e-6f;
+#pragma unroll
+          for (int nt = b * TPB; nt < (b + 1) * TPB; ++nt) {
+            const float y0 = ldexpf(acc[nt][2 * h], -ei), y1 = ldexpf(acc[nt][2 * h + 1], -ei);
+            mask[h] |= (code_e2m1(y0 - tb) != code_e2m1(y0 + tb)) ? (1u << (2 * nt)) : 0u;
+            mask[h] |= (code_e2m1(y1 - tb) != code_e2m1(y1 + tb)) ? (2u << (2 * nt)) : 0u;
+            const uint32_t c01 = code_e2m1(y0) | (code_e2m1(y1) << 8);
+            *reinterpret_cast<uint16_t*>(srow + 8 * nt + 2 * t4) = live[h] ? (uint16_t)c01 : (uint16_t)0;
           }
         }
-        amb &= ~exact;
+        if (t4 == 0 && r < rows)
+          *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.scales) + (size_t)out_row(r) * (a.o_stride / 32) + g * 4) = e_bytes;
       }
-      resolve16(wq, amb & 0xFFFFu, 0, v, r, t4, x32, p32);
-      resolve16(wq, amb & 0xFFFF0000u, 16, v, r, t4, x32, p32);
-      exact |= amb;
-      uint32_t c[32];
+      if (!live[h]) mask[h] = 0;
+    }
+    resolve<MODE, 2>(smem, mask, rbase, t4);
+  }
+
+  // ---- coalesced copy-out of the staged tile
+  if (MODE == DMOQ_A16) {
+    for (int i = tid; i < kRows * 16; i += kThreads) {
+      const int r = i >> 4, ch = i & 15;
+      if (r < rows)
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.codes) + ((size_t)out_row(r) * a.o_stride + (size_t)g * kG) * 2 + ch * 16) =
+            *reinterpret_cast<const uint4*>(stage + r * kPitchH + ch * 16);
+    }
+  } else if (MODE == DMOQ_FP4) {   // two staged one-byte codes -> one output byte, even column in the low nibble
+    for (int i = tid; i < kRows * 4; i += kThreads) {
+      const int r = i >> 2, ch = i & 3;
+      if (r < rows) {
+        const uint4 lo = *reinterpret_cast<const uint4*>(stage + r * kPitchQ + ch * 32);
+        const uint4 hi = *reinterpret_cast<const uint4*>(stage + r * kPitchQ + ch * 32 + 16);
+        const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        uint32_t o[4];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        // chain values go through the IEEE quotient exactly as the definition does; for the others the
-        // test above guarantees that the approximate quotient rounds to the same code
-        const float q = ((exact >> i) & 1u) ? __fdiv_rn(v[i], s) : v[i] * inv_s;
-        c[i] = live ? ((MODE == DMOQ_A8) ? code_i8(q) : code_e4m3(q)) : 0u;
-      }
-#pragma unroll
-      for (int nt = 0; nt < 16; ++nt)
-        *reinterpret_cast<uint16_t*>(srow + 8 * nt + 2 * t4) = (uint16_t)(c[2 * nt] | (c[2 * nt + 1] << 8));
-      if (t4 == 0 && r < rows)
-        reinterpret_cast<__half*>(a.scales)[(size_t)out_row(r) * (a.o_stride / kG) + g] = __float2half_rn(__fmul_rn(s, a.extra_scale));
-    } else {  // FP4: four 32-column blocks per row, 8 values of each block per thread
-      float mb[4], thr[4];
-      uint32_t exact = 0;
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        float m = 0.f;
-#pragma unroll
-        for (int i = 8 * b; i < 8 * b + 8; ++i) m = fmaxf(m, fabsf(v[i]));
-        mb[b] = quad_max(m);
-        thr[b] = live ? mb[b] - 2.f * delta : 3.0e38f;
-#pragma unroll
-        for (int i = 8 * b; i < 8 * b + 8; ++i) exact |= (fabsf(v[i]) >= thr[b]) ? (1u << i) : 0u;
-      }
-      resolve16(wq, exact & 0xFFFFu, 0, v, r, t4, x32, p32);
-      resolve16(wq, exact & 0xFFFF0000u, 16, v, r, t4, x32, p32);
-      uint32_t e_bytes = 0, amb = 0;
-      int ei[4];
-      float tb[4];
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        float cm = 0.f;
-#pragma unroll
-        for (int i = 8 * b; i < 8 * b + 8; ++i) cm = ((exact >> i) & 1u) ? fmaxf(cm, fabsf(v[i])) : cm;
-        const float amax = fmaxf(quad_max(cm), 1e-30f);
-        float e = ceilf((float)log2((double)__fdiv_rn(amax, 6.0f)));
-        e = fminf(fmaxf(e, -127.f), 127.f);
-        ei[b] = (int)e;
-        e_bytes |= (uint32_t)(ei[b] + 127) << (8 * b);
-        tb[b] = ldexpf(delta, -ei[b]) * 1.001f + 1e-6f;
-        if (live) {
-#pragma unroll
-          for (int i = 8 * b; i < 8 * b + 8; ++i) {
-            const float y = ldexpf(v[i], -ei[b]);
-            amb |= (code_e2m1(y - tb[b]) != code_e2m1(y + tb[b])) ? (1u << i) : 0u;
-          }
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t a0 = w[2 * j] | (w[2 * j] >> 4), a1 = w[2 * j + 1] | (w[2 * j + 1] >> 4);   // bytes 0 and 2 hold the pairs
+          o[j] = (a0 & 0xFFu) | ((a0 >> 8) & 0xFF00u) | ((a1 & 0xFFu) << 16) | ((a1 << 8) & 0xFF000000u);
         }
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.codes) + (size_t)out_row(r) * (a.o_stride / 2) + (size_t)g * 64 + ch * 16) =
+            make_uint4(o[0], o[1], o[2], o[3]);
       }
-      amb &= ~exact;
-      resolve16(wq, amb & 0xFFFFu, 0, v, r, t4, x32, p32);
-      resolve16(wq, amb & 0xFFFF0000u, 16, v, r, t4, x32, p32);
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        const int b = i >> 3;
-        const uint32_t n0 = live ? code_e2m1(ldexpf(v[i], -ei[b])) : 0u;
-        const uint32_t n1 = live ? code_e2m1(ldexpf(v[i + 1], -ei[b])) : 0u;
-        srow[(8 * (i >> 1) + 2 * t4) >> 1] = (uint8_t)(n0 | (n1 << 4));
-      }
-      if (t4 == 0 && r < rows)
-        *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.scales) + (size_t)out_row(r) * (a.o_stride / 32) + g * 4) = e_bytes;
+    }
+  } else {
+    for (int i = tid; i < kRows * 8; i += kThreads) {
+      const int r = i >> 3, ch = i & 7;
+      if (r < rows)
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.codes) + (size_t)out_row(r) * a.o_stride + (size_t)g * kG + ch * 16) =
+            *reinterpret_cast<const uint4*>(stage + r * kPitchQ + ch * 16);
     }
   }
+  __syncthreads();  // tiles, tables and the staged output are rewritten by the next block
+}
+
+// x tile + row norms + cleared maxima for the next row block; ends with a block-wide barrier.
+template <typename RowSrc>
+__device__ __forceinline__ void stage_x(const RotArgs& a, uint8_t* smem, int g, RowSrc row_src) {
+  stage_matrix(smem + kOff_x16, reinterpret_cast<float*>(smem + kOff_n2), a.x, a.src_is_bf16, (size_t)a.x_stride,
+               (size_t)g * kG, row_src);
+  reinterpret_cast<uint2*>(smem + kOff_rowmax)[threadIdx.x] = make_uint2(0u, 0u);
   __syncthreads();
-  // ---- coalesced copy-out of the staged codes
-  constexpr int CH = ROWB / 16;
-  const size_t row_bytes = (MODE == DMOQ_A16) ? (size_t)a.o_stride * 2 : (MODE == DMOQ_FP4) ? (size_t)a.o_stride / 2 : (size_t)a.o_stride;
-  for (int i = tid; i < kRows * CH; i += kThreads) {
-    const int r = i / CH, ch = i % CH;
-    if (r < rows)
-      *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.codes) + (size_t)out_row(r) * row_bytes + (size_t)g * ROWB + ch * 16) =
-          *reinterpret_cast<const uint4*>(x16 + r * ROWB + ch * 16);
-  }
-  __syncthreads();  // the staging tile is rewritten by the next block's x
 }
 
 __device__ __forceinline__ void stage_rotation(uint8_t* smem, const uint16_t* mat) {
-  stage_matrix(smem + kOff_p16, reinterpret_cast<float*>(smem + kOff_p32), nullptr, mat, 0, kG, 0,
-               [](int r) { return (long long)r; });
+  stage_matrix(smem + kOff_p16, nullptr, mat, 0, kG, 0, [](int r) { return (long long)r; });
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(kThreads, 1) rotq_mma_rows_kernel(RotArgs a) {
+__global__ void __launch_bounds__(kThreads, 2) rotq_mma_rows_kernel(RotArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int g = blockIdx.x;
   const int n_rows = a.n_rows_dev ? min(*a.n_rows_dev, a.n_rows) : a.n_rows;
@@ -344,17 +405,13 @@ __global__ void __launch_bounds__(kThreads, 1) rotq_mma_rows_kernel(RotArgs a) {
   stage_rotation(smem, a.rot + (size_t)g * kG * kG);
   for (int b = blockIdx.y; b < n_blocks; b += gridDim.y) {
     const int row0 = b * kRows, rows = min(kRows, n_rows - row0);
-    stage_matrix(smem + kOff_x16, reinterpret_cast<float*>(smem + kOff_x32), reinterpret_cast<float*>(smem + kOff_n2),
-                 a.x, a.src_is_bf16, (size_t)a.x_stride, (size_t)g * kG, [&](int r) {
-                   return r < rows ? (long long)(a.src_row ? a.src_row[row0 + r] : row0 + r) : -1LL;
-                 });
-    __syncthreads();
+    stage_x(a, smem, g, [&](int r) { return r < rows ? (long long)(a.src_row ? a.src_row[row0 + r] : row0 + r) : -1LL; });
     rotq_mma_block<MODE>(a, smem, g, rows, [&](int r) { return row0 + r; });
   }
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(kThreads, 1) rotq_mma_tiles_kernel(RotArgs a) {
+__global__ void __launch_bounds__(kThreads, 2) rotq_mma_tiles_kernel(RotArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
   const int g = blockIdx.x;
   const int n_tiles = a.n_tiles[a.pool];
@@ -363,16 +420,13 @@ __global__ void __launch_bounds__(kThreads, 1) rotq_mma_tiles_kernel(RotArgs a) 
   for (int t = blockIdx.y; t < n_tiles; t += gridDim.y) {
     const DmoqTile tile = tiles[t];
     const int mat = tile.rank * a.groups_per_member + g;
-    if (mat != loaded) {
+    if (mat != loaded) {   // every thread left the previous block through its closing barrier
       stage_rotation(smem, a.rot + (size_t)mat * kG * kG);
       loaded = mat;
     }
     for (int r0 = 0; r0 < tile.rows; r0 += kRows) {
       const int row0 = tile.row0 + r0, rows = min(kRows, tile.rows - r0);
-      stage_matrix(smem + kOff_x16, reinterpret_cast<float*>(smem + kOff_x32), reinterpret_cast<float*>(smem + kOff_n2),
-                   a.x, a.src_is_bf16, (size_t)a.x_stride, (size_t)g * kG,
-                   [&](int r) { return r < rows ? (long long)(row0 + r) : -1LL; });
-      __syncthreads();
+      stage_x(a, smem, g, [&](int r) { return r < rows ? (long long)(row0 + r) : -1LL; });
       rotq_mma_block<MODE>(a, smem, g, rows, [&](int r) { return row0 + r; });
     }
   }
@@ -388,7 +442,7 @@ int launch_rows(const RotArgs& a, cudaStream_t s) {
   }
   const int G = a.K / kG;
   const int n_blocks = dmoq_ceil_div(a.n_rows, kRows);
-  int gy = dmoq_ceil_div(dmoq_sm_count(), G);
+  int gy = dmoq_ceil_div(2 * dmoq_sm_count(), G);
   if (gy > n_blocks) gy = n_blocks;
   if (gy < 1) gy = 1;
   rotq_mma_rows_kernel<MODE><<<dim3(G, gy), kThreads, kSmem, s>>>(a);
@@ -404,7 +458,7 @@ int launch_tiles(const RotArgs& a, int tile_cap, cudaStream_t s) {
     configured = true;
   }
   const int G = a.K / kG;
-  int gy = dmoq_ceil_div(dmoq_sm_count(), G);
+  int gy = dmoq_ceil_div(2 * dmoq_sm_count(), G);
   if (gy > tile_cap) gy = tile_cap;
   if (gy < 1) gy = 1;
   rotq_mma_tiles_kernel<MODE><<<dim3(G, gy), kThreads, kSmem, s>>>(a);
