@@ -4,17 +4,17 @@
 //   warps 0-7   epilogue: drain the per-group accumulator from TMEM (tcgen05.ld), fold
 //               (acc * row_scale) * col_norm into an fp32 running total, final SiLU*up or
 //               routing-weight epilogue through a padded shared-memory staging tile
-//   warps 8-11  producers: gather activation-code rows with cp.async straight into the 128B-swizzled
+//   warps 8-15  producers: gather activation-code rows with cp.async straight into the 128B-swizzled
 //               K-major operand tile; copy the packed codebook indices with cp.async into a raw ring
 //               and expand them in registers (byte-permute lookups) into the swizzled B operand tile;
 //               they also stage each group's row scales and column norms into a small ring
-//   warp 12     one elected thread issues tcgen05.mma (M=128, N=128, K=32 x4 per 128-wide group),
+//   warp 16     one elected thread issues tcgen05.mma (M=128, N=128, K=32 x4 per 128-wide group),
 //               tcgen05.commit releases the smem stage and publishes the accumulator
-//   warps 13-15 idle (they only give their registers away: setmaxnreg moves them to the epilogue)
+//   warps 17-19 idle (they only give their registers away: setmaxnreg works on whole warpgroups)
 // Tile metadata and row indices of the NEXT work item are fetched while the current one runs, so the
 // operand pipeline does not drain at item boundaries.
-// Accumulators are double-buffered in TMEM (2 x 128 columns), so the tensor pipe works on group g+1
-// while the epilogue warps scale group g.  Integer group sums are exact (kind::i8, int32), which is
+// Four accumulator buffers fill TMEM (4 x 128 columns), so the tensor pipe runs up to three groups ahead
+// of the epilogue warps (it keeps going while they write out a finished tile).  Integer group sums are exact (kind::i8, int32), which is
 // what turboquant_utils/triton_kernels_a8.py:893-929 computes; kind::f8f6f4 gives the fp32 group sums of
 // turboquant_utils/triton_kernels_fp8.py:589-626.
 //
@@ -27,10 +27,20 @@ namespace {
 constexpr int kBM = 128, kBN = 128, kG = DMOQ_GROUP;
 constexpr int kStages = 4;       // operand ring depth (one 128-wide group per stage)
 constexpr int kLag = 2;          // producer: stages between issuing the async copies and expanding them
-constexpr int kEpiWarps = 8, kProdWarps = 4;
-constexpr int kThreads = 512;     // 4 warpgroups: epilogue, epilogue, producers, MMA (+3 idle warps)
-constexpr int kScaleRing = 8;     // per-group scale slots; must exceed kStages + 2 (see the epilogue)
-constexpr int kRegsEpi = 176, kRegsProd = 104, kRegsMma = 40;   // 256*176 + 128*104 + 128*40 <= 65536
+constexpr int kEpiWarps = 8, kProdWarps = 8;
+constexpr int kProdThreads = 32 * kProdWarps;
+constexpr int kCPT = kBM * 8 / kProdThreads;   // 16-byte operand chunks per producer thread, tile and stage (4)
+constexpr int kThreads = 640;     // 5 warpgroups: epilogue x2, producers x2, MMA warp + 3 idle warps
+constexpr int kAccBufs = 4;       // accumulator buffers in TMEM
+constexpr int kScaleRing = 16;    // per-group scale slots; must exceed kStages + kAccBufs (see the epilogue)
+// setmaxnreg moves registers between the warpgroups inside the pool the block got at launch: 640 threads x the
+// 96 registers ptxas reports for this kernel.  Asking for more than the pool holds blocks forever, so the
+// launch helper refuses to run if the compiled kernel's register count is not kRegsLaunch.
+constexpr int kRegsLaunch = 96;
+constexpr int kRegsEpi = 168, kRegsProd = 56, kRegsMma = 24;
+static_assert(32 * (kEpiWarps * kRegsEpi + kProdWarps * kRegsProd + 4 * kRegsMma) <= kRegsLaunch * kThreads,
+              "role register budgets exceed the block's register pool");
+static_assert(kThreads == 32 * (kEpiWarps + kProdWarps + 4) && kEpiWarps % 4 == 0 && kProdWarps % 4 == 0, "role layout");
 constexpr int kTileB = kBM * kG; // bytes of one int8 / e4m3 operand tile
 constexpr int kOutPitch = 272;   // bytes per staged output row (256 + 16: conflict-free 16-byte stores)
 constexpr uint32_t kSpinLimit = 1u << 26;
@@ -41,6 +51,23 @@ constexpr uint32_t kMagicBits = 0x4B400000u;
 constexpr float kMagicFloat = 12582912.0f;
 
 __device__ int g_dmoq_tc_status = 0;
+
+// Optional per-role cycle counters (block 0, first warp of each role); compiled in only for tuning builds.
+#ifdef DMOQ_TC_PROFILE
+__device__ unsigned long long g_tc_prof[32];
+#define PROF_DECL long long prof_t0 = 0, prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define PROF_BEGIN() prof_t0 = clock64()
+#define PROF_END(i) prof_acc[i] += clock64() - prof_t0
+#define PROF_FLUSH(base, cond)                                                        \
+  if ((cond) && blockIdx.x == 0 && lane == 0) {                                       \
+    for (int i_ = 0; i_ < 8; ++i_) atomicAdd(&g_tc_prof[(base) + i_], (unsigned long long)prof_acc[i_]); \
+  }
+#else
+#define PROF_DECL
+#define PROF_BEGIN()
+#define PROF_END(i)
+#define PROF_FLUSH(base, cond)
+#endif
 
 struct TcArgs {
   const DmoqTile* tiles;
@@ -79,17 +106,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait (about one second of SM clock).  Returns false, and raises the abort flag, if the phase
-// never completes; once the flag is up every later wait returns at once.
+// Same, but the hardware may keep the thread suspended for up to `ns` nanoseconds while the phase is pending,
+// so a waiting warp does not compete for issue slots and shared-memory bandwidth.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait (about one second).  Returns false, and raises the abort flag, if the phase never completes;
+// once the flag is up every later wait returns at once.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
   if (*abort_flag) return false;
   const long long t0 = clock64();
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 63u) == 63u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) break;
-    }
+    if (mbar_try_wait_suspend(bar, parity, 100000u)) return true;   // <= 0.1 ms per try
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) break;
   }
   *abort_flag = 1;
   atomicOr(&g_dmoq_tc_status, 1);
@@ -130,6 +169,19 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+// 16 lanes x 64 columns: register 4m+2h+e of thread t = lane base + t/4 + 8h, column base + 8m + 2(t%4) + e
+__device__ __forceinline__ void tc_ld16x256(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // 32 lanes x 32 columns of one 32-bit value
 __device__ __forceinline__ void tc_st32_fill(uint32_t taddr, uint32_t v) {
@@ -138,6 +190,10 @@ __device__ __forceinline__ void tc_st32_fill(uint32_t taddr, uint32_t v) {
       "{%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};"
       ::"r"(taddr), "r"(v)
       : "memory");
+}
+// 32 lanes x 8 columns: the narrow form keeps only 8 registers busy where the caller is short of them
+__device__ __forceinline__ void tc_st8_fill(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(taddr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // packed fp32 pairs (each lane IEEE round-to-nearest, unfused)
@@ -155,14 +211,6 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
       "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
       : "=f"(d.x), "=f"(d.y)
       : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-  return d;
-}
-__device__ __forceinline__ float2 add2(float2 a, float2 b) {
-  float2 d;
-  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
   return d;
 }
 __device__ __forceinline__ void bar_sync_epi() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory"); }
@@ -214,12 +262,12 @@ __device__ __forceinline__ uint4 expand16(const uint32_t* raw, const Lut& lut, b
       o[2 * h + 1] = prmt(lo_b, hi_b, (hi >> 16) | 0x3210u);
     }
   } else if (BIT == 2) {  // raw[0] = 16 two-bit fields
+    const uint32_t w = raw[0], w4 = raw[0] >> 4;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      uint32_t s = (raw[0] >> (16 * h)) & 0xFFFFu;
-      s = (s | (s << 8)) & 0x00FF00FFu;
-      s = (s | (s << 4)) & 0x0F0F0F0Fu;
-      s = (s | (s << 2)) & 0x33333333u;
+      // bytes (w.b, (w>>4).b, w.b', (w>>4).b'): the low nibble of each holds two fields; spread them to one per nibble
+      const uint32_t u = prmt(w, w4, h ? 0x7362u : 0x5140u) & 0x0F0F0F0Fu;
+      const uint32_t s = (u | (u << 2)) & 0x33333333u;
       o[2 * h + 0] = prmt(lut.w[0], lut.w[0], s);
       o[2 * h + 1] = prmt(lut.w[0], lut.w[0], s >> 16);
     }
@@ -245,7 +293,7 @@ struct Smem {
   uint8_t out[kBM * kOutPitch];
   float sc_norm[kScaleRing][kBN];   // column norms of a group, tile column order
   float sc_xs[kScaleRing][kBM];     // row scales of a group
-  uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2], sc_full[kScaleRing];
+  uint64_t full[kStages], empty[kStages], acc_full[kAccBufs], acc_empty[kAccBufs], sc_full[kScaleRing];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -270,7 +318,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       mbar_init(&S.full[s], kProdWarps);
       mbar_init(&S.empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kAccBufs; ++b) {
       mbar_init(&S.acc_full[b], 1);
       mbar_init(&S.acc_empty[b], kEpiWarps);
     }
@@ -280,7 +328,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
   }
   if (warp == kMmaWarp) {  // the MMA warp owns the TMEM allocation
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&S.tmem_base)),
-                 "r"(2 * kBN));
+                 "r"(kAccBufs * kBN));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   tc_fence_before();
@@ -288,10 +336,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
   tc_fence_after();
   const uint32_t tmem_base = S.tmem_base;
   if (MODE == DMOQ_A8) {
-    if (warp < kEpiWarps) {  // bias both accumulator buffers
+    if (warp < kEpiWarps) {  // bias every accumulator buffer
       const uint32_t t0 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (warp >> 2) * 64;
 #pragma unroll
-      for (int b = 0; b < 2; ++b) {
+      for (int b = 0; b < kAccBufs; ++b) {
         tc_st32_fill(t0 + b * kBN, kMagicBits);
         tc_st32_fill(t0 + b * kBN + 32, kMagicBits);
       }
@@ -318,89 +366,121 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
 
   if (warp < kEpiWarps) {
     // =========================================================================== epilogue warps
+    // Accumulators are read with the 16x256b shape (the fragment layout of an m16n8 MMA accumulator): thread t of
+    // a warp holds, for each of its four rows  quarter*32 + t/4 + 8j  (j = 0..3), the sixteen columns
+    // half*64 + 8m + 2(t%4) + {0,1}  (m = 0..7).  A thread therefore needs only 16 column norms per group
+    // (8-byte loads shared by the lanes of equal t%4) instead of 64 warp-wide broadcast loads.
     reg_inc<kRegsEpi>();
     const int quarter = warp & 3, half = warp >> 2;
-    const int r = quarter * 32 + lane;               // tile row == TMEM lane
     const int etid = warp * 32 + lane;
+    const int t4 = lane & 3;
+    const int row_b = quarter * 32 + (lane >> 2);      // rows row_b + 8j
+    const int col_b = half * 64 + 2 * t4;              // tile columns col_b + 8m + e
     uint32_t ia = 0;                                  // groups consumed so far
     DmoqTile next = tile_of(0);
+    PROF_DECL;
+#ifdef DMOQ_TC_PROFILE
+    const long long prof_start = clock64();
+#endif
     for (int item = 0; item < n_items; ++item) {
       const DmoqTile tile = next;
       next = tile_of(item + 1);                       // in flight while this item is processed
       const int nb = (blockIdx.x + item * stride_w) % NB;
-      const bool row_ok = r < tile.rows;
-      const int grow = tile.row0 + r;
-      float wgt = 0.f;
-      if (EPI == DMOQ_EPI_WEIGHTED && row_ok) wgt = a.row_weight[grow];
 
-      float2 total2[32];
+      float2 total2[32];                              // [j][m]: columns (e = 0, 1) of row j, column block m
 #pragma unroll
       for (int c = 0; c < 32; ++c) total2[c] = make_float2(0.f, 0.f);
 
       for (int g = 0; g < G; ++g, ++ia) {
-        const uint32_t b = ia & 1, ph = (ia >> 1) & 1;
+        const uint32_t b = ia % kAccBufs, ph = (ia / kAccBufs) & 1;
         const uint32_t slot = ia % kScaleRing;
-        // A scale slot is rewritten kScaleRing groups later; the producers can be at most kStages + 2 groups
+        // A scale slot is rewritten kScaleRing groups later; the producers can be at most kStages + kAccBufs groups
         // ahead of the group whose accumulator this warp has released, so the slot is still intact here.
+        PROF_BEGIN();
         mbar_wait(&S.sc_full[slot], (ia / kScaleRing) & 1, abort_flag);
+        PROF_END(0);
+        PROF_BEGIN();
         mbar_wait(&S.acc_full[b], ph, abort_flag);    // on a timeout the flag is up and the data is void
+        PROF_END(1);
         tc_fence_after();
+        PROF_BEGIN();
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + b * kBN + half * 64;
-        const float xs = S.sc_xs[slot][r];
-        const float2 xs2 = make_float2(xs, xs);
-        const float2 unbias = make_float2(-kMagicFloat, -kMagicFloat);
-        const float4* nrm4 = reinterpret_cast<const float4*>(&S.sc_norm[slot][half * 64]);
-        const int n_out = a.is_down ? a.hidden : 2 * a.inter;
+        uint32_t v0[32], v1[32];                      // rows j = 0,1 and j = 2,3
+        tc_ld16x256(taddr, v0);
+        tc_ld16x256(taddr + (16u << 16), v1);
+        float xs[4];
 #pragma unroll
-        for (int part = 0; part < 2; ++part) {   // two 32-column loads keep the register footprint down
-          uint32_t v[32];
-          tc_ld32(taddr + part * 32, v);
-          tc_wait_ld();
-          if (MODE == DMOQ_A8) tc_st32_fill(taddr + part * 32, kMagicBits);  // re-arm the bias for the next use
-          if (part == 1) {                         // the accumulator buffer can be overwritten now
-            if (MODE == DMOQ_A8) tc_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&S.acc_empty[b]);
-          }
+        for (int j = 0; j < 4; ++j) xs[j] = S.sc_xs[slot][row_b + 8 * j];
+        float off[4];
 #pragma unroll
-          for (int c4 = 0; c4 < 8; ++c4) {
-            const float4 nv = nrm4[part * 8 + c4];
+        for (int j = 0; j < 4; ++j) off[j] = -kMagicFloat * xs[j];
+        const float2* nrm2 = reinterpret_cast<const float2*>(&S.sc_norm[slot][col_b]);
+        tc_wait_ld();
+        PROF_END(4);
+        PROF_BEGIN();
+        if (MODE == DMOQ_A8) {   // re-arm the bias for the buffer's next use
 #pragma unroll
-            for (int h2 = 0; h2 < 2; ++h2) {
-              const int c = c4 * 4 + h2 * 2;
-              float2 f = make_float2(__uint_as_float(v[c]), __uint_as_float(v[c + 1]));
-              if (MODE == DMOQ_A8) f = add2(f, unbias);
-              const float2 n2 = h2 ? make_float2(nv.z, nv.w) : make_float2(nv.x, nv.y);
-              const int t = part * 16 + c4 * 2 + h2;
-              total2[t] = fma2(mul2(f, xs2), n2, total2[t]);   // (acc*xs)*norm + total, last step fused
+          for (int q = 0; q < 8; ++q) tc_st8_fill(taddr + 8 * q, kMagicBits);
+          tc_wait_st();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&S.acc_empty[b]);   // the accumulator buffer can be overwritten now
+        PROF_END(5);
+        PROF_BEGIN();
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+          const float2 n2 = nrm2[4 * m];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t(&v)[32] = (j >> 1) ? v1 : v0;
+            const int i = 4 * m + 2 * (j & 1);
+            const float fx = __uint_as_float(v[i]), fy = __uint_as_float(v[i + 1]);
+            float2 t2;
+            if (MODE == DMOQ_A8) {   // (acc_biased - M) * xs in one fma with the exact constant -M*xs (2 x 11 significant bits)
+              t2 = make_float2(fmaf(fx, xs[j], off[j]), fmaf(fy, xs[j], off[j]));
+            } else {
+              t2 = make_float2(__fmul_rn(fx, xs[j]), __fmul_rn(fy, xs[j]));
             }
+            total2[j * 8 + m] = fma2(t2, n2, total2[j * 8 + m]);   // (acc*xs)*norm + total, last step fused
           }
-          if (MODE == DMOQ_A8 && a.partials != nullptr && row_ok) {
+        }
+        if (MODE == DMOQ_A8 && a.partials != nullptr) {
+          const int n_out = a.is_down ? a.hidden : 2 * a.inter;
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              const int col = half * 64 + part * 32 + c;
-              const int n = a.is_down ? nb * kBN + col : (col & 1) * a.inter + nb * (kBN / 2) + (col >> 1);
-              a.partials[((size_t)grow * n_out + n) * G + g] = (int32_t)(v[c] - kMagicBits);
+          for (int j = 0; j < 4; ++j) {
+            const int row = row_b + 8 * j;
+            if (row < tile.rows) {
+              const uint32_t(&v)[32] = (j >> 1) ? v1 : v0;
+#pragma unroll
+              for (int m = 0; m < 8; ++m)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                  const int col = col_b + 8 * m + e;
+                  const int n = a.is_down ? nb * kBN + col : (col & 1) * a.inter + nb * (kBN / 2) + (col >> 1);
+                  a.partials[((size_t)(tile.row0 + row) * n_out + n) * G + g] = (int32_t)(v[4 * m + 2 * (j & 1) + e] - kMagicBits);
+                }
             }
           }
         }
+        PROF_END(6);
       }
 
       // ---- tile epilogue through the staging tile
+      PROF_BEGIN();
       if (EPI == DMOQ_EPI_SILU) {
-        __align__(16) __half o[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float gate = __half2float(__float2half_rn(total2[i].x));
-          const float up = __half2float(__float2half_rn(total2[i].y));
-          const float sg = __half2float(__float2half_rn(__fdiv_rn(gate, 1.0f + expf(-gate))));
-          o[i] = __float2half_rn(__fmul_rn(sg, up));
-        }
         bar_sync_epi();  // the previous item's copy-out has finished reading the staging tile
 #pragma unroll
-        for (int q = 0; q < 4; ++q)
-          *reinterpret_cast<uint4*>(&S.out[r * kOutPitch + half * 64 + q * 16]) = reinterpret_cast<const uint4*>(o)[q];
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int m = 0; m < 8; ++m) {
+            const float gate = __half2float(__float2half_rn(total2[j * 8 + m].x));
+            const float up = __half2float(__float2half_rn(total2[j * 8 + m].y));
+            // fast exp and reciprocal (a few fp32 ulps) ahead of the fp16 rounding: a floating-point stage
+            const float sg = __half2float(__float2half_rn(__fdividef(gate, 1.0f + __expf(-gate))));
+            *reinterpret_cast<__half*>(&S.out[(row_b + 8 * j) * kOutPitch + (half * 32 + 4 * m + t4) * 2]) =
+                __float2half_rn(__fmul_rn(sg, up));
+          }
         bar_sync_epi();
         __half* out = reinterpret_cast<__half*>(a.out);
         for (int i = etid; i < kBM * 8; i += 32 * kEpiWarps) {
@@ -411,30 +491,43 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
         }
       } else if (EPI == DMOQ_EPI_PLAIN && !a.is_down) {
         __half* out = reinterpret_cast<__half*>(a.out);
-        if (row_ok) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) {
-            const int col = half * 64 + c;
-            const int n = (col & 1) * a.inter + nb * (kBN / 2) + (col >> 1);
-            out[(size_t)grow * a.out_stride + n] = __float2half_rn((c & 1) ? total2[c >> 1].y : total2[c >> 1].x);
+        for (int j = 0; j < 4; ++j) {
+          const int row = row_b + 8 * j;
+          if (row < tile.rows) {
+#pragma unroll
+            for (int m = 0; m < 8; ++m) {
+              const int oc = nb * (kBN / 2) + half * 32 + 4 * m + t4;   // gate column; the up column is inter further
+              out[(size_t)(tile.row0 + row) * a.out_stride + oc] = __float2half_rn(total2[j * 8 + m].x);
+              out[(size_t)(tile.row0 + row) * a.out_stride + a.inter + oc] = __float2half_rn(total2[j * 8 + m].y);
+            }
           }
         }
       } else {
-        __align__(16) uint16_t o[64];
-#pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const __half h16 = __float2half_rn((c & 1) ? total2[c >> 1].y : total2[c >> 1].x);
-          if (EPI == DMOQ_EPI_WEIGHTED) {
-            const __nv_bfloat16 bb = __float2bfloat16_rn(__half2float(h16));
-            o[c] = __bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(__bfloat162float(bb), wgt)));
-          } else {
-            o[c] = __half_as_ushort(h16);
-          }
-        }
         bar_sync_epi();
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
-          *reinterpret_cast<uint4*>(&S.out[r * kOutPitch + half * 128 + q * 16]) = reinterpret_cast<const uint4*>(o)[q];
+        for (int j = 0; j < 4; ++j) {
+          const int row = row_b + 8 * j;
+          float wgt = 0.f;
+          if (EPI == DMOQ_EPI_WEIGHTED && row < tile.rows) wgt = a.row_weight[tile.row0 + row];
+#pragma unroll
+          for (int m = 0; m < 8; ++m) {
+            uint32_t pk = 0;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const __half h16 = __float2half_rn(e ? total2[j * 8 + m].y : total2[j * 8 + m].x);
+              uint32_t o16;
+              if (EPI == DMOQ_EPI_WEIGHTED) {
+                const __nv_bfloat16 bb = __float2bfloat16_rn(__half2float(h16));
+                o16 = __bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(__bfloat162float(bb), wgt)));
+              } else {
+                o16 = __half_as_ushort(h16);
+              }
+              pk |= o16 << (16 * e);
+            }
+            *reinterpret_cast<uint32_t*>(&S.out[row * kOutPitch + (col_b + 8 * m) * 2]) = pk;
+          }
+        }
         bar_sync_epi();
         uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
         for (int i = etid; i < kBM * 16; i += 32 * kEpiWarps) {
@@ -444,33 +537,41 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
                 *reinterpret_cast<const uint4*>(&S.out[rr * kOutPitch + ch * 16]);
         }
       }
+      PROF_END(2);
     }
+#ifdef DMOQ_TC_PROFILE
+    prof_acc[3] = clock64() - prof_start;
+#endif
+    PROF_FLUSH(0, warp == 0);
   } else if (warp < kMmaWarp) {
     // =========================================================================== producer warps
     reg_dec<kRegsProd>();
-    const int pt = tid - 32 * kEpiWarps;              // 0..127: also the tile row / column whose scale it stages
+    const int pt = tid - 32 * kEpiWarps;              // 0..255
     Lut lut;
 #pragma unroll
     for (int q = 0; q < 4; ++q) lut.w[q] = 0;
     if (!(BIT == 8)) {
       for (int i = 0; i < (1 << BIT); ++i) lut.w[i >> 2] |= (uint32_t)a.lut[i] << (8 * (i & 3));
     }
-    // chunk ownership: 8 (row, 16-byte chunk) pairs per thread and stage, chosen so that a warp's
+    // chunk ownership: kCPT (row, 16-byte chunk) pairs per thread and stage, chosen so that a warp's
     // stores fall on distinct shared-memory bank groups
-    auto own_row = [&](int i) { return (BIT == 1) ? (pt >> 2) + 32 * (i >> 1) : (pt >> 3) + 16 * i; };
+    auto own_row = [&](int i) { return (BIT == 1) ? (pt >> 2) + 64 * (i >> 1) : (pt >> 3) + 32 * i; };
     auto own_chunk = [&](int i) { return (BIT == 1) ? 2 * (pt & 3) + (i & 1) : (pt & 7); };
     const int xs_per_row = a.a_stride / kG;
+    // threads 0-127 stage the row scale of tile row pt, threads 128-255 the norm of tile column pt - 128
+    const bool stages_xs = pt < kBM;
+    const int sc_i = pt & (kBM - 1);
 
-    // scale values travel in registers from the issue of a group to its publication kLag groups later
-    uint16_t xs_q[kLag + 1], nm_q[kLag + 1];
+    // the scale value travels in a register from the issue of a group to its publication kLag groups later
+    uint16_t sc_q[kLag + 1];
 #pragma unroll
-    for (int i = 0; i <= kLag; ++i) xs_q[i] = nm_q[i] = 0;
+    for (int i = 0; i <= kLag; ++i) sc_q[i] = 0;
 
-    auto publish = [&](uint32_t j, int qi) {   // qi: position of group j's scales in the register queue
+    auto publish = [&](uint32_t j, int qi) {   // qi: position of group j's scale in the register queue
       const int s = j % kStages;
       if (BIT != 8) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < kCPT; ++i) {
           const int row = own_row(i), ch = own_chunk(i);
           uint32_t raw[2];
           if (BIT == 4) {
@@ -487,7 +588,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < kCPT; ++i) {
           uint4* p = reinterpret_cast<uint4*>(&S.b[s][swz128(own_row(i), own_chunk(i))]);
           uint4 v = *p;
           uint32_t raw[4] = {v.x, v.y, v.z, v.w};
@@ -495,16 +596,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
         }
       }
       const uint32_t slot = j % kScaleRing;
-      uint16_t xs_h = xs_q[0], nm_h = nm_q[0];
+      uint16_t sc_h = sc_q[0];
 #pragma unroll
       for (int i = 1; i <= kLag; ++i) {
-        if (qi == i) {
-          xs_h = xs_q[i];
-          nm_h = nm_q[i];
-        }
+        if (qi == i) sc_h = sc_q[i];
       }
-      S.sc_xs[slot][pt] = __half2float(__ushort_as_half(xs_h));
-      S.sc_norm[slot][pt] = __half2float(__ushort_as_half(nm_h));
+      (stages_xs ? S.sc_xs[slot] : S.sc_norm[slot])[sc_i] = __half2float(__ushort_as_half(sc_h));
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) {
@@ -513,23 +610,27 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       }
     };
 
-    // row bookkeeping of one work item: table rows this thread copies (8) and the row whose scale it stages
+    // row bookkeeping of one work item: table rows this thread copies and the row whose scale it stages
     struct Rows {
-      int cp[8];
+      int cp[kCPT];
       int own;
     };
     auto rows_of = [&](const DmoqTile& t) {
       Rows rw;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int rr = (pt >> 3) + 16 * i;
+      for (int i = 0; i < kCPT; ++i) {
+        const int rr = (pt >> 3) + 32 * i;
         rw.cp[i] = rr < t.rows ? (a.a_row ? a.a_row[t.row0 + rr] : t.row0 + rr) : -1;
       }
-      rw.own = pt < t.rows ? (a.a_row ? a.a_row[t.row0 + pt] : t.row0 + pt) : -1;
+      rw.own = (stages_xs && sc_i < t.rows) ? (a.a_row ? a.a_row[t.row0 + sc_i] : t.row0 + sc_i) : -1;
       return rw;
     };
 
     uint32_t it = 0, done = 0;
+    PROF_DECL;
+#ifdef DMOQ_TC_PROFILE
+    const long long prof_start = clock64();
+#endif
     DmoqTile t_next = tile_of(0), t_next2 = tile_of(1);
     Rows r_next = rows_of(t_next);
     for (int item = 0; item < n_items; ++item) {
@@ -542,26 +643,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       const int gg0 = a.is_down ? tile.rank * G : 0;
       const int seg0 = a.is_down ? nb * kBN : tile.rank * 2 * a.inter + nb * (kBN / 2);
       const int seg1 = a.is_down ? seg0 : seg0 + a.inter;
-      const int own_n = a.is_down ? seg0 + pt : ((pt & 1) ? seg1 : seg0) + (pt >> 1);
+      const int own_n = a.is_down ? seg0 + sc_i : ((sc_i & 1) ? seg1 : seg0) + (sc_i >> 1);
       for (int g = 0; g < G; ++g, ++it) {
         const int s = it % kStages;
+        PROF_BEGIN();
         mbar_wait(&S.empty[s], ((it / kStages) & 1) ^ 1, abort_flag);
+        PROF_END(0);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int rr = (pt >> 3) + 16 * i, ch = pt & 7;
+        for (int i = 0; i < kCPT; ++i) {
+          const int rr = (pt >> 3) + 32 * i, ch = pt & 7;
           const uint8_t* src = a.a_codes + (size_t)(rw.cp[i] < 0 ? 0 : rw.cp[i]) * a.a_stride + (size_t)g * kG + ch * 16;
           cp_async16_zfill(&S.a[s][swz128(rr, ch)], src, rw.cp[i] >= 0);
         }
         if (BIT == 1) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {  // one 4-byte copy covers two adjacent chunks
-            const int row = (pt >> 2) + 32 * i, pair = pt & 3;
+          for (int i = 0; i < kCPT / 2; ++i) {  // one 4-byte copy covers two adjacent chunks
+            const int row = (pt >> 2) + 64 * i, pair = pt & 3;
             const int n = a.is_down ? seg0 + row : ((row & 1) ? seg1 : seg0) + (row >> 1);
             cp_async_n(&S.raw[s][row * BPG + pair * 4], a.idx + ((size_t)(gg0 + g) * n_total + n) * BPG + pair * 4, 4);
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < kCPT; ++i) {
             const int row = own_row(i), ch = own_chunk(i);
             const int n = a.is_down ? seg0 + row : ((row & 1) ? seg1 : seg0) + (row >> 1);
             const uint8_t* src = a.idx + ((size_t)(gg0 + g) * n_total + n) * BPG + ch * RAWB;
@@ -570,17 +673,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
           }
         }
         cp_async_commit();
-        // scales of this group: loaded now, stored when the group is published
+        // scale of this group: loaded now, stored when the group is published
 #pragma unroll
-        for (int i = kLag; i > 0; --i) {
-          xs_q[i] = xs_q[i - 1];
-          nm_q[i] = nm_q[i - 1];
-        }
-        xs_q[0] = rw.own >= 0 ? a.a_scales[(size_t)rw.own * xs_per_row + g] : (uint16_t)0;
-        nm_q[0] = a.norm[(size_t)(gg0 + g) * n_total + own_n];
+        for (int i = kLag; i > 0; --i) sc_q[i] = sc_q[i - 1];
+        if (stages_xs) sc_q[0] = rw.own >= 0 ? a.a_scales[(size_t)rw.own * xs_per_row + g] : (uint16_t)0;
+        else sc_q[0] = a.norm[(size_t)(gg0 + g) * n_total + own_n];
         if (it - done >= (uint32_t)kLag) {
+          PROF_BEGIN();
           cp_async_wait<kLag>();
+          PROF_END(1);
+          PROF_BEGIN();
           publish(done++, kLag);
+          PROF_END(2);
         }
       }
     }
@@ -591,6 +695,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       publish(done, (int)pending);
       ++done;
     }
+#ifdef DMOQ_TC_PROFILE
+    prof_acc[3] = clock64() - prof_start;
+#endif
+    PROF_FLUSH(8, warp == kEpiWarps);
   } else {
     reg_dec<kRegsMma>();
     if (warp == kMmaWarp) {
@@ -598,11 +706,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       constexpr uint32_t idesc_i8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
       constexpr uint32_t idesc_f8 = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
       const uint32_t total_groups = (uint32_t)n_items * (uint32_t)G;
+      PROF_DECL;
+#ifdef DMOQ_TC_PROFILE
+      const long long prof_start = clock64();
+#endif
       for (uint32_t it = 0; it < total_groups; ++it) {
         const int s = it % kStages;
-        const uint32_t b = it & 1;
+        const uint32_t b = it % kAccBufs;
+        PROF_BEGIN();
         bool ok = mbar_wait(&S.full[s], (it / kStages) & 1, abort_flag);
-        ok = mbar_wait(&S.acc_empty[b], ((it >> 1) & 1) ^ 1, abort_flag) && ok;
+        PROF_END(0);
+        PROF_BEGIN();
+        ok = mbar_wait(&S.acc_empty[b], ((it / kAccBufs) & 1) ^ 1, abort_flag) && ok;
+        PROF_END(1);
         tc_fence_after();
         if (lane == 0 && ok) {
           const uint64_t da = make_desc(smem_u32(&S.a[s][0]));
@@ -618,6 +734,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
         }
         __syncwarp();
       }
+#ifdef DMOQ_TC_PROFILE
+      prof_acc[3] = clock64() - prof_start;
+#endif
+      PROF_FLUSH(16, true);
     }
   }
 
@@ -626,7 +746,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
   __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * kBN));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kAccBufs * kBN));
   }
 }
 
@@ -635,6 +755,9 @@ int launch(const TcArgs& a, int work_cap, cudaStream_t s) {
   static bool configured = false;
   const int bytes = (int)sizeof(Smem) + 1024;
   if (!configured) {
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, gemm_tc_kernel<MODE, BIT, EPI>) != cudaSuccess) return DMOQ_ELAUNCH;
+    if (fa.numRegs != kRegsLaunch) return DMOQ_ELAUNCH;   // the role budgets were sized for this pool
     if (cudaFuncSetAttribute(gemm_tc_kernel<MODE, BIT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
       return DMOQ_ELAUNCH;
     configured = true;
@@ -707,6 +830,17 @@ int dmoq_grouped_gemm_tc(const dmoq_route_t* route, const dmoq_pool_t& p, int po
   if (p.mode == DMOQ_A8) return launch_bit<DMOQ_A8>(a, p.bit, epilogue, work_cap, s);
   return launch_bit<DMOQ_FP8>(a, p.bit, epilogue, work_cap, s);
 }
+
+#ifdef DMOQ_TC_PROFILE
+extern "C" int dmoq_tc_profile(unsigned long long* out32, int reset) {
+  if (cudaMemcpyFromSymbol(out32, g_tc_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return DMOQ_EDEVICE;
+  if (reset) {
+    unsigned long long z[32] = {0};
+    if (cudaMemcpyToSymbol(g_tc_prof, z, sizeof(z)) != cudaSuccess) return DMOQ_EDEVICE;
+  }
+  return DMOQ_OK;
+}
+#endif
 
 // Device status word of the tensor-core kernels: 0 = no bounded wait has ever timed out on this device.
 extern "C" int dmoq_tc_status(int32_t* status_host) {
