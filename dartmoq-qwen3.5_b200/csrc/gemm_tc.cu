@@ -157,18 +157,6 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
       : "memory");
 }
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
 // 16 lanes x 64 columns: register 4m+2h+e of thread t = lane base + t/4 + 8h, column base + 8m + 2(t%4) + e
 __device__ __forceinline__ void tc_ld16x256(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -197,14 +185,6 @@ __device__ __forceinline__ void tc_st8_fill(uint32_t taddr, uint32_t v) {
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // packed fp32 pairs (each lane IEEE round-to-nearest, unfused)
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
-  float2 d;
-  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-      "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
   float2 d;
   asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
@@ -293,7 +273,7 @@ struct Smem {
   uint8_t out[kBM * kOutPitch];
   float sc_norm[kScaleRing][kBN];   // column norms of a group, tile column order
   float sc_xs[kScaleRing][kBM];     // row scales of a group
-  uint64_t full[kStages], empty[kStages], acc_full[kAccBufs], acc_empty[kAccBufs], sc_full[kScaleRing];
+  uint64_t full[kStages], empty[kStages], acc_full[kAccBufs], acc_empty[kAccBufs];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -322,7 +302,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       mbar_init(&S.acc_full[b], 1);
       mbar_init(&S.acc_empty[b], kEpiWarps);
     }
-    for (int i = 0; i < kScaleRing; ++i) mbar_init(&S.sc_full[i], kProdWarps);
     S.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -394,11 +373,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       for (int g = 0; g < G; ++g, ++ia) {
         const uint32_t b = ia % kAccBufs, ph = (ia / kAccBufs) & 1;
         const uint32_t slot = ia % kScaleRing;
-        // A scale slot is rewritten kScaleRing groups later; the producers can be at most kStages + kAccBufs groups
-        // ahead of the group whose accumulator this warp has released, so the slot is still intact here.
-        PROF_BEGIN();
-        mbar_wait(&S.sc_full[slot], (ia / kScaleRing) & 1, abort_flag);
-        PROF_END(0);
+        // The group's scales were stored before its producers arrived on full[]; the MMA warp saw that arrival
+        // before it committed acc_full[], so they are visible here.  A slot is rewritten kScaleRing groups later and
+        // the producers run at most kStages + kAccBufs groups ahead of an unreleased accumulator: still intact.
         PROF_BEGIN();
         mbar_wait(&S.acc_full[b], ph, abort_flag);    // on a timeout the flag is up and the data is void
         PROF_END(1);
@@ -512,18 +489,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
           if (EPI == DMOQ_EPI_WEIGHTED && row < tile.rows) wgt = a.row_weight[tile.row0 + row];
 #pragma unroll
           for (int m = 0; m < 8; ++m) {
-            uint32_t pk = 0;
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const __half h16 = __float2half_rn(e ? total2[j * 8 + m].y : total2[j * 8 + m].x);
-              uint32_t o16;
-              if (EPI == DMOQ_EPI_WEIGHTED) {
-                const __nv_bfloat16 bb = __float2bfloat16_rn(__half2float(h16));
-                o16 = __bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(__bfloat162float(bb), wgt)));
-              } else {
-                o16 = __half_as_ushort(h16);
-              }
-              pk |= o16 << (16 * e);
+            uint32_t pk;
+            const __half2 h2 = __floats2half2_rn(total2[j * 8 + m].x, total2[j * 8 + m].y);   // the fp16 output
+            if (EPI == DMOQ_EPI_WEIGHTED) {   // -> bf16, times the routing weight in fp32, -> bf16
+              const float2 hf = __half22float2(h2);
+              const float2 bf = __bfloat1622float2(__floats2bfloat162_rn(hf.x, hf.y));
+              const __nv_bfloat162 o2 = __floats2bfloat162_rn(__fmul_rn(bf.x, wgt), __fmul_rn(bf.y, wgt));
+              pk = *reinterpret_cast<const uint32_t*>(&o2);
+            } else {
+              pk = *reinterpret_cast<const uint32_t*>(&h2);
             }
             *reinterpret_cast<uint32_t*>(&S.out[row * kOutPitch + (col_b + 8 * m) * 2]) = pk;
           }
@@ -604,10 +578,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       (stages_xs ? S.sc_xs[slot] : S.sc_norm[slot])[sc_i] = __half2float(__ushort_as_half(sc_h));
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&S.sc_full[slot]);
-        mbar_arrive(&S.full[s]);
-      }
+      if (lane == 0) mbar_arrive(&S.full[s]);
     };
 
     // row bookkeeping of one work item: table rows this thread copies and the row whose scale it stages
