@@ -4,6 +4,7 @@
 ``kernels``  function-level operators over libdmoq (the C ABI in include/dmoq.h)
 ``moe``      WxA16 / WxA8 / WxFP8 / WxFP4 BitPartitionedGroupMoE modules
 ``linear``   packed dense Linear layers (shared expert)
+``host_io``  pipelined layer calls over pinned host batches
 ``synth``    seeded synthetic layers of the benchmark shapes
 ``build``    nvcc build of libdmoq.so
 """

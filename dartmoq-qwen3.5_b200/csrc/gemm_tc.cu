@@ -43,6 +43,7 @@ static_assert(32 * (kEpiWarps * kRegsEpi + kProdWarps * kRegsProd + 4 * kRegsMma
 static_assert(kThreads == 32 * (kEpiWarps + kProdWarps + 4) && kEpiWarps % 4 == 0 && kProdWarps % 4 == 0, "role layout");
 constexpr int kTileB = kBM * kG; // bytes of one int8 / e4m3 operand tile
 constexpr int kOutPitch = 272;   // bytes per staged output row (256 + 16: conflict-free 16-byte stores)
+constexpr int kRawPad = 64;     // bytes between the gate and the up segment of the raw index tile (bank spread)
 constexpr uint32_t kSpinLimit = 1u << 26;
 constexpr long long kWaitCycles = 2000000000LL;
 // INT8 accumulators start from the bit pattern of 1.5*2^23: the int32 sum read back as fp32 is then
@@ -133,6 +134,25 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   *abort_flag = 1;
   atomicOr(&g_dmoq_tc_status, 1);
   return false;
+}
+// One thread announces `bytes` of bulk-copy traffic on the barrier (and arrives on it) ...
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// ... and starts the copies: global -> this block's shared memory, completion counted in bytes on the barrier.
+// Both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+// Time-bounded wait that ignores the abort flag: used at teardown so that no bulk copy is still writing into
+// this block's shared memory when it exits.
+__device__ __forceinline__ void mbar_wait_quiet(uint64_t* bar, uint32_t parity) {
+  const long long t0 = clock64();
+  while (!mbar_try_wait_suspend(bar, parity, 100000u)) {
+    if (clock64() - t0 > kWaitCycles) break;
+  }
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -269,11 +289,11 @@ struct Smem {
   // operand ring, 1024-byte aligned tiles
   uint8_t a[kStages][kTileB];
   uint8_t b[kStages][kTileB];
-  uint8_t raw[kStages][kBN * 64];   // packed indices of one group (<= 64 bytes per row: 4-bit)
+  uint8_t raw[kStages][kBN * 64 + kRawPad];   // packed indices of one group (<= 64 bytes per row: 4-bit), two segments
   uint8_t out[kBM * kOutPitch];
   float sc_norm[kScaleRing][kBN];   // column norms of a group, tile column order
   float sc_xs[kScaleRing][kBM];     // row scales of a group
-  uint64_t full[kStages], empty[kStages], acc_full[kAccBufs], acc_empty[kAccBufs];
+  uint64_t full[kStages], empty[kStages], acc_full[kAccBufs], acc_empty[kAccBufs], raw_full[kStages];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -297,6 +317,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&S.full[s], kProdWarps);
       mbar_init(&S.empty[s], 1);
+      mbar_init(&S.raw_full[s], 1);
     }
     for (int b = 0; b < kAccBufs; ++b) {
       mbar_init(&S.acc_full[b], 1);
@@ -390,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
         for (int j = 0; j < 4; ++j) xs[j] = S.sc_xs[slot][row_b + 8 * j];
         float off[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) off[j] = -kMagicFloat * xs[j];
+        for (int j = 0; j < 4; ++j) off[j] = (MODE == DMOQ_A8) ? -kMagicFloat * xs[j] : 0.f;
         const float2* nrm2 = reinterpret_cast<const float2*>(&S.sc_norm[slot][col_b]);
         tc_wait_ld();
         PROF_END(4);
@@ -412,13 +433,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
           for (int j = 0; j < 4; ++j) {
             const uint32_t(&v)[32] = (j >> 1) ? v1 : v0;
             const int i = 4 * m + 2 * (j & 1);
-            const float fx = __uint_as_float(v[i]), fy = __uint_as_float(v[i + 1]);
-            float2 t2;
-            if (MODE == DMOQ_A8) {   // (acc_biased - M) * xs in one fma with the exact constant -M*xs (2 x 11 significant bits)
-              t2 = make_float2(fmaf(fx, xs[j], off[j]), fmaf(fy, xs[j], off[j]));
-            } else {
-              t2 = make_float2(__fmul_rn(fx, xs[j]), __fmul_rn(fy, xs[j]));
-            }
+            const float2 f = make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+            // INT8: (acc_biased - M) * xs in one fma with the exact constant -M*xs (2 x 11 significant bits);
+            // e4m3: acc * xs (adding +0 changes nothing: the product is never -0 unless acc is, and then total decides)
+            const float2 t2 = fma2(f, make_float2(xs[j], xs[j]), make_float2(off[j], off[j]));
             total2[j * 8 + m] = fma2(t2, n2, total2[j * 8 + m]);   // (acc*xs)*norm + total, last step fused
           }
         }
@@ -531,11 +549,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
     // stores fall on distinct shared-memory bank groups
     auto own_row = [&](int i) { return (BIT == 1) ? (pt >> 2) + 64 * (i >> 1) : (pt >> 3) + 32 * i; };
     auto own_chunk = [&](int i) { return (BIT == 1) ? 2 * (pt & 3) + (i & 1) : (pt & 7); };
+    // Packed indices arrive by bulk copy: gate_up tiles as two 64-row segments (gate rows, then up rows, kRawPad
+    // bytes apart), down tiles as one 128-row segment.  Tile row -> byte offset of its BPG index bytes:
+    auto raw_off = [&](int row) {
+      return a.is_down ? row * BPG : ((row & 1) * (64 * BPG + kRawPad) + (row >> 1) * BPG);
+    };
     const int xs_per_row = a.a_stride / kG;
     // threads 0-127 stage the row scale of tile row pt, threads 128-255 the norm of tile column pt - 128
     const bool stages_xs = pt < kBM;
     const int sc_i = pt & (kBM - 1);
 
+    PROF_DECL;
     // the scale value travels in a register from the issue of a group to its publication kLag groups later
     uint16_t sc_q[kLag + 1];
 #pragma unroll
@@ -544,18 +568,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
     auto publish = [&](uint32_t j, int qi) {   // qi: position of group j's scale in the register queue
       const int s = j % kStages;
       if (BIT != 8) {
+        mbar_wait(&S.raw_full[s], (j / kStages) & 1, abort_flag);   // the bulk copy of this group's indices has landed
 #pragma unroll
         for (int i = 0; i < kCPT; ++i) {
           const int row = own_row(i), ch = own_chunk(i);
           uint32_t raw[2];
           if (BIT == 4) {
-            const uint2 v = *reinterpret_cast<const uint2*>(&S.raw[s][row * BPG + ch * 8]);
+            const uint2 v = *reinterpret_cast<const uint2*>(&S.raw[s][raw_off(row) + ch * 8]);
             raw[0] = v.x;
             raw[1] = v.y;
           } else if (BIT == 2) {
-            raw[0] = *reinterpret_cast<const uint32_t*>(&S.raw[s][row * BPG + ch * 4]);
+            raw[0] = *reinterpret_cast<const uint32_t*>(&S.raw[s][raw_off(row) + ch * 4]);
           } else {
-            const uint32_t v = *reinterpret_cast<const uint32_t*>(&S.raw[s][row * BPG + (ch >> 1) * 4]);
+            const uint32_t v = *reinterpret_cast<const uint32_t*>(&S.raw[s][raw_off(row) + (ch >> 1) * 4]);
             raw[0] = (ch & 1) ? (v >> 16) : (v & 0xFFFFu);
           }
           *reinterpret_cast<uint4*>(&S.b[s][swz128(row, ch)]) = expand16<BIT>(raw, lut, false);
@@ -576,9 +601,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
         if (qi == i) sc_h = sc_q[i];
       }
       (stages_xs ? S.sc_xs[slot] : S.sc_norm[slot])[sc_i] = __half2float(__ushort_as_half(sc_h));
+#ifdef DMOQ_TC_PROFILE
+      const long long prof_f0 = clock64();
+#endif
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.full[s]);
+#ifdef DMOQ_TC_PROFILE
+      prof_acc[7] += clock64() - prof_f0;
+#endif
     };
 
     // row bookkeeping of one work item: table rows this thread copies and the row whose scale it stages
@@ -598,7 +629,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
     };
 
     uint32_t it = 0, done = 0;
-    PROF_DECL;
 #ifdef DMOQ_TC_PROFILE
     const long long prof_start = clock64();
 #endif
@@ -620,35 +650,41 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
         PROF_BEGIN();
         mbar_wait(&S.empty[s], ((it / kStages) & 1) ^ 1, abort_flag);
         PROF_END(0);
+        PROF_BEGIN();
 #pragma unroll
         for (int i = 0; i < kCPT; ++i) {
           const int rr = (pt >> 3) + 32 * i, ch = pt & 7;
           const uint8_t* src = a.a_codes + (size_t)(rw.cp[i] < 0 ? 0 : rw.cp[i]) * a.a_stride + (size_t)g * kG + ch * 16;
           cp_async16_zfill(&S.a[s][swz128(rr, ch)], src, rw.cp[i] >= 0);
         }
-        if (BIT == 1) {
-#pragma unroll
-          for (int i = 0; i < kCPT / 2; ++i) {  // one 4-byte copy covers two adjacent chunks
-            const int row = (pt >> 2) + 64 * i, pair = pt & 3;
-            const int n = a.is_down ? seg0 + row : ((row & 1) ? seg1 : seg0) + (row >> 1);
-            cp_async_n(&S.raw[s][row * BPG + pair * 4], a.idx + ((size_t)(gg0 + g) * n_total + n) * BPG + pair * 4, 4);
-          }
-        } else {
+        PROF_END(4);
+        PROF_BEGIN();
+        if (BIT == 8) {   // 8-bit indices go straight into the operand tile (expanded in place)
 #pragma unroll
           for (int i = 0; i < kCPT; ++i) {
             const int row = own_row(i), ch = own_chunk(i);
             const int n = a.is_down ? seg0 + row : ((row & 1) ? seg1 : seg0) + (row >> 1);
-            const uint8_t* src = a.idx + ((size_t)(gg0 + g) * n_total + n) * BPG + ch * RAWB;
-            if (BIT == 8) cp_async_n(&S.b[s][swz128(row, ch)], src, 16);
-            else cp_async_n(&S.raw[s][row * BPG + ch * RAWB], src, RAWB);
+            cp_async_n(&S.b[s][swz128(row, ch)], a.idx + ((size_t)(gg0 + g) * n_total + n) * BPG + ch * RAWB, 16);
+          }
+        } else if (pt == 0) {   // one thread moves the group's packed indices with bulk copies
+          const uint8_t* gsrc = a.idx + (size_t)(gg0 + g) * n_total * BPG;
+          mbar_arrive_expect_tx(&S.raw_full[s], kBN * BPG);
+          if (a.is_down) {
+            bulk_g2s(&S.raw[s][0], gsrc + (size_t)seg0 * BPG, kBN * BPG, &S.raw_full[s]);
+          } else {
+            bulk_g2s(&S.raw[s][0], gsrc + (size_t)seg0 * BPG, 64 * BPG, &S.raw_full[s]);
+            bulk_g2s(&S.raw[s][64 * BPG + kRawPad], gsrc + (size_t)seg1 * BPG, 64 * BPG, &S.raw_full[s]);
           }
         }
         cp_async_commit();
+        PROF_END(5);
+        PROF_BEGIN();
         // scale of this group: loaded now, stored when the group is published
 #pragma unroll
         for (int i = kLag; i > 0; --i) sc_q[i] = sc_q[i - 1];
         if (stages_xs) sc_q[0] = rw.own >= 0 ? a.a_scales[(size_t)rw.own * xs_per_row + g] : (uint16_t)0;
         else sc_q[0] = a.norm[(size_t)(gg0 + g) * n_total + own_n];
+        PROF_END(6);
         if (it - done >= (uint32_t)kLag) {
           PROF_BEGIN();
           cp_async_wait<kLag>();
@@ -665,6 +701,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       if (pending >= 1) cp_async_wait<1>(); else cp_async_wait<0>();
       publish(done, (int)pending);
       ++done;
+    }
+    if (BIT != 8 && pt == 0) {   // no bulk copy may still be in flight when the block exits (matters after an abort)
+      for (uint32_t j = (it > (uint32_t)kStages ? it - kStages : 0u); j < it; ++j)
+        mbar_wait_quiet(&S.raw_full[j % kStages], (j / kStages) & 1);
     }
 #ifdef DMOQ_TC_PROFILE
     prof_acc[3] = clock64() - prof_start;

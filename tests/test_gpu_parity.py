@@ -464,6 +464,22 @@ def test_small_batch_graph_replay_matches_eager(mode):
     assert rel_fro(outs[0].float().cpu().numpy(), ref) < TOL[mode]
 
 
+def test_host_streamer_matches_direct_calls():
+    """Pinned host batches through the three-stream pipeline give the results of plain module calls."""
+    from dartmoq_b200.host_io import HostStreamer
+    moe = _layer("wxa8", seed=12).to(DEV)
+    T = 300
+    xs = [synth.make_activations(T, 256, seed=70 + i).pin_memory() for i in range(5)]
+    ys = [torch.empty(T, 256, dtype=torch.bfloat16).pin_memory() for _ in xs]
+    st = HostStreamer(moe, T, 256, DEV)
+    for x, y in zip(xs, ys):
+        st.submit(x, y)
+    st.join()
+    torch.cuda.synchronize()
+    for x, y in zip(xs, ys):
+        assert torch.equal(y, moe(x.to(DEV).unsqueeze(0))[0].cpu())
+
+
 def test_zz_tensor_core_status_word_is_clean():
     """No bounded wait of the tcgen05 kernels ran out during this session."""
     import ctypes
