@@ -10,7 +10,8 @@
 //               they also stage each group's row scales and column norms into a small ring
 //   warp 16     one elected thread issues tcgen05.mma (M=128, N=128, K=32 x4 per 128-wide group),
 //               tcgen05.commit releases the smem stage and publishes the accumulator
-//   warps 17-19 idle (they only give their registers away: setmaxnreg works on whole warpgroups)
+//   warp 17     one thread bulk-copies each group's packed indices into the raw ring
+//   warps 18-19 idle (they only give their registers away: setmaxnreg works on whole warpgroups)
 // Tile metadata and row indices of the NEXT work item are fetched while the current one runs, so the
 // operand pipeline does not drain at item boundaries.
 // Four accumulator buffers fill TMEM (4 x 128 columns), so the tensor pipe runs up to three groups ahead
@@ -666,15 +667,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
             const int n = a.is_down ? seg0 + row : ((row & 1) ? seg1 : seg0) + (row >> 1);
             cp_async_n(&S.b[s][swz128(row, ch)], a.idx + ((size_t)(gg0 + g) * n_total + n) * BPG + ch * RAWB, 16);
           }
-        } else if (pt == 0) {   // one thread moves the group's packed indices with bulk copies
-          const uint8_t* gsrc = a.idx + (size_t)(gg0 + g) * n_total * BPG;
-          mbar_arrive_expect_tx(&S.raw_full[s], kBN * BPG);
-          if (a.is_down) {
-            bulk_g2s(&S.raw[s][0], gsrc + (size_t)seg0 * BPG, kBN * BPG, &S.raw_full[s]);
-          } else {
-            bulk_g2s(&S.raw[s][0], gsrc + (size_t)seg0 * BPG, 64 * BPG, &S.raw_full[s]);
-            bulk_g2s(&S.raw[s][64 * BPG + kRawPad], gsrc + (size_t)seg1 * BPG, 64 * BPG, &S.raw_full[s]);
-          }
         }
         cp_async_commit();
         PROF_END(5);
@@ -701,10 +693,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       if (pending >= 1) cp_async_wait<1>(); else cp_async_wait<0>();
       publish(done, (int)pending);
       ++done;
-    }
-    if (BIT != 8 && pt == 0) {   // no bulk copy may still be in flight when the block exits (matters after an abort)
-      for (uint32_t j = (it > (uint32_t)kStages ? it - kStages : 0u); j < it; ++j)
-        mbar_wait_quiet(&S.raw_full[j % kStages], (j / kStages) & 1);
     }
 #ifdef DMOQ_TC_PROFILE
     prof_acc[3] = clock64() - prof_start;
@@ -749,6 +737,36 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       prof_acc[3] = clock64() - prof_start;
 #endif
       PROF_FLUSH(16, true);
+    } else if (warp == kMmaWarp + 1 && BIT != 8) {
+      // ========================================================================= index loader
+      // One thread moves each group's packed indices into the raw ring with bulk copies as soon as the stage is
+      // free: gate_up tiles as two 64-row segments (gate rows, up rows), down tiles as one 128-row segment.
+      if (lane == 0) {
+        uint32_t it = 0;
+        for (int item = 0; item < n_items; ++item) {
+          const DmoqTile tile = tile_of(item);
+          const int nb = (blockIdx.x + item * stride_w) % NB;
+          const int gg0 = a.is_down ? tile.rank * G : 0;
+          const int seg0 = a.is_down ? nb * kBN : tile.rank * 2 * a.inter + nb * (kBN / 2);
+          for (int g = 0; g < G; ++g, ++it) {
+            const int s = it % kStages;
+            if (!mbar_wait(&S.empty[s], ((it / kStages) & 1) ^ 1, abort_flag)) break;
+            const uint8_t* gsrc = a.idx + ((size_t)(gg0 + g) * n_total + seg0) * BPG;
+            mbar_arrive_expect_tx(&S.raw_full[s], kBN * BPG);
+            if (a.is_down) {
+              bulk_g2s(&S.raw[s][0], gsrc, kBN * BPG, &S.raw_full[s]);
+            } else {
+              bulk_g2s(&S.raw[s][0], gsrc, 64 * BPG, &S.raw_full[s]);
+              bulk_g2s(&S.raw[s][64 * BPG + kRawPad], gsrc + (size_t)a.inter * BPG, 64 * BPG, &S.raw_full[s]);
+            }
+          }
+          if (*abort_flag) break;
+        }
+        // no bulk copy may still be in flight when the block exits (matters after an abort)
+        for (uint32_t j = (it > (uint32_t)kStages ? it - kStages : 0u); j < it; ++j)
+          mbar_wait_quiet(&S.raw_full[j % kStages], (j / kStages) & 1);
+      }
+      __syncwarp();
     }
   }
 
