@@ -30,6 +30,7 @@ class Pool(C.Structure):
         ("gu_act_scale", C.c_float), ("dn_act_scale", C.c_float),
         ("gu_rot", C.c_void_p), ("dn_rot", C.c_void_p),
         ("act_codes", C.c_void_p), ("act_scales", C.c_void_p),
+        ("gu_idx_wide", C.c_void_p), ("dn_idx_wide", C.c_void_p),
     ]
 
 
@@ -65,6 +66,7 @@ EXPORTS = {
     "dmoq_tc_status": (C.c_int, [C.POINTER(C.c_int32)]),
     "dmoq_combine": (C.c_int, [C.POINTER(Route), C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "dmoq_convert_group_first": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "dmoq_widen_indices": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
 }
 
 _lib = None

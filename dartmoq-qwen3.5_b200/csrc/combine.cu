@@ -47,7 +47,36 @@ __global__ void group_first_kernel(const uint8_t* __restrict__ src, uint8_t* __r
   }
 }
 
+// every 1- or 2-bit code -> one 4-bit field, low field first; one packed byte per thread and step
+template <int BIT>
+__global__ void widen_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, long long n_bytes) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_bytes; i += (long long)gridDim.x * blockDim.x) {
+    const uint32_t b = src[i];
+    if (BIT == 2) {   // c0 c1 c2 c3 -> bytes (c0 | c1 << 4), (c2 | c3 << 4)
+      const uint32_t lo = (b & 3u) | ((b & 0xCu) << 2), hi = ((b >> 4) & 3u) | ((b >> 2) & 0x30u);
+      *reinterpret_cast<uint16_t*>(dst + 2 * i) = (uint16_t)(lo | (hi << 8));
+    } else {          // eight one-bit codes -> four bytes
+      uint32_t w = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) w |= ((b >> k) & 1u) << (4 * k);
+      *reinterpret_cast<uint32_t*>(dst + 4 * i) = w;
+    }
+  }
+}
+
 }  // namespace
+
+extern "C" int dmoq_widen_indices(const uint8_t* packed, int64_t n_bytes, int32_t bit, uint8_t* wide, void* stream) {
+  DMOQ_CHECK_ARG(packed && wide && n_bytes >= 0 && (bit == 1 || bit == 2));
+  if (n_bytes == 0) return DMOQ_OK;
+  long long blocks = (n_bytes + 255) / 256;
+  const long long cap = 16LL * dmoq_sm_count();
+  if (blocks > cap) blocks = cap;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bit == 2) widen_kernel<2><<<(int)blocks, 256, 0, s>>>(packed, wide, n_bytes);
+  else widen_kernel<1><<<(int)blocks, 256, 0, s>>>(packed, wide, n_bytes);
+  return dmoq_launch_status();
+}
 
 extern "C" int dmoq_combine(const dmoq_route_t* route, const uint16_t* dn, int32_t hidden,
                             void* y, int32_t y_is_bf16, void* stream) {

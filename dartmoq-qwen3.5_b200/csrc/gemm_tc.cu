@@ -5,9 +5,10 @@
 //               (acc * row_scale) * col_norm into an fp32 running total, final SiLU*up or
 //               routing-weight epilogue through a padded shared-memory staging tile
 //   warps 8-15  producers: gather activation-code rows with cp.async straight into the 128B-swizzled
-//               K-major operand tile; copy the packed codebook indices with cp.async into a raw ring
-//               and expand them in registers (byte-permute lookups) into the swizzled B operand tile;
-//               they also stage each group's row scales and column norms into a small ring
+//               K-major operand tile; look the codebook indices of the raw ring up in registers (byte
+//               permutes; 1- and 2-bit codes are stored widened to 4-bit fields for this) and store the
+//               codewords into the swizzled B operand tile; they also stage each group's row scales and
+//               column norms into a small ring
 //   warp 16     one elected thread issues tcgen05.mma (M=128, N=128, K=32 x4 per 128-wide group),
 //               tcgen05.commit releases the smem stage and publishes the accumulator
 //   warp 17     one thread bulk-copies each group's packed indices into the raw ring
@@ -205,15 +206,8 @@ __device__ __forceinline__ void tc_st8_fill(uint32_t taddr, uint32_t v) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(taddr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-// packed fp32 pairs (each lane IEEE round-to-nearest, unfused)
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-  float2 d;
-  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
-      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-  return d;
-}
+// packed fp32 pairs (each half an IEEE round-to-nearest fma)
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
 __device__ __forceinline__ void bar_sync_epi() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory"); }
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
   uint32_t d;
@@ -262,26 +256,11 @@ __device__ __forceinline__ uint4 expand16(const uint32_t* raw, const Lut& lut, b
       o[2 * h + 0] = prmt(lo_a, hi_a, (hi & 0xFFFFu) | 0x3210u);
       o[2 * h + 1] = prmt(lo_b, hi_b, (hi >> 16) | 0x3210u);
     }
-  } else if (BIT == 2) {  // raw[0] = 16 two-bit fields
-    const uint32_t w = raw[0], w4 = raw[0] >> 4;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      // bytes (w.b, (w>>4).b, w.b', (w>>4).b'): the low nibble of each holds two fields; spread them to one per nibble
-      const uint32_t u = prmt(w, w4, h ? 0x7362u : 0x5140u) & 0x0F0F0F0Fu;
-      const uint32_t s = (u | (u << 2)) & 0x33333333u;
-      o[2 * h + 0] = prmt(lut.w[0], lut.w[0], s);
-      o[2 * h + 1] = prmt(lut.w[0], lut.w[0], s >> 16);
-    }
-  } else {  // BIT == 1: low 16 bits of raw[0]
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      uint32_t s = (raw[0] >> (8 * h)) & 0xFFu;
-      s = (s | (s << 12)) & 0x000F000Fu;
-      s = (s | (s << 6)) & 0x03030303u;
-      s = (s | (s << 3)) & 0x11111111u;
-      o[2 * h + 0] = prmt(lut.w[0], lut.w[0], s);
-      o[2 * h + 1] = prmt(lut.w[0], lut.w[0], s >> 16);
-    }
+  } else {  // 1- and 2-bit pools arrive widened: raw[0..1] = 16 four-bit fields, each holding one code
+    o[0] = prmt(lut.w[0], lut.w[0], raw[0]);        // prmt reads the low four selector nibbles only
+    o[1] = prmt(lut.w[0], lut.w[0], raw[0] >> 16);
+    o[2] = prmt(lut.w[0], lut.w[0], raw[1]);
+    o[3] = prmt(lut.w[0], lut.w[0], raw[1] >> 16);
   }
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
@@ -310,8 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   volatile int* abort_flag = &S.abort_flag;
-  constexpr int BPG = 16 * BIT;                       // packed bytes per row per group
-  constexpr int RAWB = (BIT == 1) ? 4 : BPG / 8;      // bytes one cp.async moves (1-bit: two chunks at once)
+  constexpr int BPG = (BIT <= 2) ? 64 : 16 * BIT;    // index bytes per row per group (1/2-bit codes come widened to 4 bits)
   constexpr int kMmaWarp = kEpiWarps + kProdWarps;
 
   if (tid == 0) {
@@ -420,11 +398,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
         if (MODE == DMOQ_A8) {   // re-arm the bias for the buffer's next use
 #pragma unroll
           for (int q = 0; q < 8; ++q) tc_st8_fill(taddr + 8 * q, kMagicBits);
-          tc_wait_st();
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&S.acc_empty[b]);   // the accumulator buffer can be overwritten now
         PROF_END(5);
         PROF_BEGIN();
 #pragma unroll
@@ -459,6 +433,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
             }
           }
         }
+        // release the accumulator buffer only now: the bias stores complete behind the scale math, and with four
+        // buffers the tensor pipe does not wait for this one
+        if (MODE == DMOQ_A8) tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&S.acc_empty[b]);
         PROF_END(6);
       }
 
@@ -548,8 +528,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
     }
     // chunk ownership: kCPT (row, 16-byte chunk) pairs per thread and stage, chosen so that a warp's
     // stores fall on distinct shared-memory bank groups
-    auto own_row = [&](int i) { return (BIT == 1) ? (pt >> 2) + 64 * (i >> 1) : (pt >> 3) + 32 * i; };
-    auto own_chunk = [&](int i) { return (BIT == 1) ? 2 * (pt & 3) + (i & 1) : (pt & 7); };
+    auto own_row = [&](int i) { return (pt >> 3) + 32 * i; };
+    auto own_chunk = [&](int) { return pt & 7; };
     // Packed indices arrive by bulk copy: gate_up tiles as two 64-row segments (gate rows, then up rows, kRawPad
     // bytes apart), down tiles as one 128-row segment.  Tile row -> byte offset of its BPG index bytes:
     auto raw_off = [&](int row) {
@@ -569,23 +549,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
     auto publish = [&](uint32_t j, int qi) {   // qi: position of group j's scale in the register queue
       const int s = j % kStages;
       if (BIT != 8) {
+#ifdef DMOQ_TC_PROFILE
+        const long long prof_r0 = clock64();
+#endif
         mbar_wait(&S.raw_full[s], (j / kStages) & 1, abort_flag);   // the bulk copy of this group's indices has landed
+#ifdef DMOQ_TC_PROFILE
+        const long long prof_r1 = clock64();
+        prof_acc[5] += prof_r1 - prof_r0;
+#endif
 #pragma unroll
         for (int i = 0; i < kCPT; ++i) {
           const int row = own_row(i), ch = own_chunk(i);
-          uint32_t raw[2];
-          if (BIT == 4) {
-            const uint2 v = *reinterpret_cast<const uint2*>(&S.raw[s][raw_off(row) + ch * 8]);
-            raw[0] = v.x;
-            raw[1] = v.y;
-          } else if (BIT == 2) {
-            raw[0] = *reinterpret_cast<const uint32_t*>(&S.raw[s][raw_off(row) + ch * 4]);
-          } else {
-            const uint32_t v = *reinterpret_cast<const uint32_t*>(&S.raw[s][raw_off(row) + (ch >> 1) * 4]);
-            raw[0] = (ch & 1) ? (v >> 16) : (v & 0xFFFFu);
-          }
+          const uint2 v = *reinterpret_cast<const uint2*>(&S.raw[s][raw_off(row) + ch * 8]);
+          const uint32_t raw[2] = {v.x, v.y};
           *reinterpret_cast<uint4*>(&S.b[s][swz128(row, ch)]) = expand16<BIT>(raw, lut, false);
         }
+#ifdef DMOQ_TC_PROFILE
+        prof_acc[6] += clock64() - prof_r1;
+#endif
       } else {
 #pragma unroll
         for (int i = 0; i < kCPT; ++i) {
@@ -659,24 +640,20 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
           cp_async16_zfill(&S.a[s][swz128(rr, ch)], src, rw.cp[i] >= 0);
         }
         PROF_END(4);
-        PROF_BEGIN();
         if (BIT == 8) {   // 8-bit indices go straight into the operand tile (expanded in place)
 #pragma unroll
           for (int i = 0; i < kCPT; ++i) {
             const int row = own_row(i), ch = own_chunk(i);
             const int n = a.is_down ? seg0 + row : ((row & 1) ? seg1 : seg0) + (row >> 1);
-            cp_async_n(&S.b[s][swz128(row, ch)], a.idx + ((size_t)(gg0 + g) * n_total + n) * BPG + ch * RAWB, 16);
+            cp_async_n(&S.b[s][swz128(row, ch)], a.idx + ((size_t)(gg0 + g) * n_total + n) * BPG + ch * 16, 16);
           }
         }
         cp_async_commit();
-        PROF_END(5);
-        PROF_BEGIN();
         // scale of this group: loaded now, stored when the group is published
 #pragma unroll
         for (int i = kLag; i > 0; --i) sc_q[i] = sc_q[i - 1];
         if (stages_xs) sc_q[0] = rw.own >= 0 ? a.a_scales[(size_t)rw.own * xs_per_row + g] : (uint16_t)0;
         else sc_q[0] = a.norm[(size_t)(gg0 + g) * n_total + own_n];
-        PROF_END(6);
         if (it - done >= (uint32_t)kLag) {
           PROF_BEGIN();
           cp_async_wait<kLag>();
@@ -825,6 +802,7 @@ int launch_bit(const TcArgs& a, int bit, int epi, int work_cap, cudaStream_t s) 
 bool dmoq_tc_supported(const dmoq_pool_t& p, int is_down, int hidden) {
   if (p.mode != DMOQ_A8 && p.mode != DMOQ_FP8) return false;
   if (p.bit == 8 && !(p.mode == DMOQ_A8 && p.identity_lut)) return false;
+  if (p.bit <= 2 && (is_down ? p.dn_idx_wide : p.gu_idx_wide) == nullptr) return false;   // needs widened indices
   const int G = is_down ? p.inter / kG : hidden / kG;
   return G >= 1;
 }
@@ -843,7 +821,7 @@ int dmoq_grouped_gemm_tc(const dmoq_route_t* route, const dmoq_pool_t& p, int po
   a.inter = p.inter;
   a.hidden = hidden;
   a.n_members = p.n_members;
-  a.idx = is_down ? p.dn_idx : p.gu_idx;
+  a.idx = p.bit <= 2 ? (is_down ? p.dn_idx_wide : p.gu_idx_wide) : (is_down ? p.dn_idx : p.gu_idx);
   a.norm = is_down ? p.dn_norm : p.gu_norm;
   a.lut = static_cast<const uint8_t*>(is_down ? p.dn_lut : p.gu_lut);
   a.identity_lut = p.identity_lut;

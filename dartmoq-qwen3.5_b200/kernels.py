@@ -208,6 +208,15 @@ def _merged(mode: int, is_down: bool, a_codes: torch.Tensor, a_scales: Optional[
     else:
         p.gu_idx, p.gu_norm, p.gu_lut, p.gu_e0 = indices_gf.data_ptr(), norms.data_ptr(), lut.data_ptr(), e0
     p.identity_lut = int(identity)
+    wide = None
+    if bit_width <= 2 and mode in (A8, FP8):   # the tensor-core kernel reads these codes widened to 4-bit fields
+        wide = torch.empty(indices_gf.shape[:2] + (64,), dtype=torch.uint8, device=dev)
+        check(lib.dmoq_widen_indices(ptr(indices_gf), indices_gf.numel(), bit_width, ptr(wide), _stream()),
+              "dmoq_widen_indices")
+        if is_down:
+            p.dn_idx_wide = wide.data_ptr()
+        else:
+            p.gu_idx_wide = wide.data_ptr()
     out = torch.empty((n_rows, n_out), dtype=out_dtype, device=dev)
     check(lib.dmoq_grouped_gemm(C.byref(route.c), pool, 0, int(is_down), epilogue, hidden,
                                 ptr(a_codes), ptr(a_scales), a_stride, ptr(out), n_out, ptr(partials), _stream()),

@@ -137,6 +137,14 @@ def _group_first_device(indices_packed: torch.Tensor, bit: int, k: int, device) 
     return dst
 
 
+def _widen_device(idx_gf: torch.Tensor, bit: int) -> torch.Tensor:
+    """Group-first 1- or 2-bit indices (G, N, 16*bit) -> (G, N, 64): one code per 4-bit field."""
+    lib = _lib.load()
+    dst = torch.empty(idx_gf.shape[:2] + (64,), dtype=torch.uint8, device=idx_gf.device)
+    check(lib.dmoq_widen_indices(ptr(idx_gf), idx_gf.numel(), bit, ptr(dst), _stream()), "dmoq_widen_indices")
+    return dst
+
+
 def _mode_lut(mode: int, bit: int, codebook: torch.Tensor, device):
     """(lut tensor, act_scale, e0, norm_factor, identity) for one codebook in one activation mode."""
     cb = codebook.detach().cpu()
@@ -171,6 +179,11 @@ class _PoolRuntime:
             raise ValueError("hidden and intermediate sizes must be multiples of 128")
         self.gu_idx = _group_first_device(gu["indices_packed"], bit, hidden, device)
         self.dn_idx = _group_first_device(dn["indices_packed"], bit, n_members * inter, device)
+        # the tensor-core GEMM (INT8 / e4m3 modes) reads 1- and 2-bit codes widened to 4-bit fields; the packed
+        # copy stays for the small-batch kernel, which is bound by the index stream
+        self.gu_idx_wide = self.dn_idx_wide = None
+        if bit <= 2 and mode in (A8, FP8):
+            self.gu_idx_wide, self.dn_idx_wide = _widen_device(self.gu_idx, bit), _widen_device(self.dn_idx, bit)
         lut_g, s_g, e0_g, f_g, ident_g = _mode_lut(mode, bit, gu["codebook"], device)
         lut_d, s_d, e0_d, f_d, ident_d = _mode_lut(mode, bit, dn["codebook"], device)
         self.gu_lut, self.dn_lut = lut_g, lut_d
@@ -199,6 +212,8 @@ class _PoolRuntime:
         c.gu_e0, c.dn_e0 = e0_g, e0_d
         c.gu_act_scale, c.dn_act_scale = s_g, s_d
         c.gu_rot, c.dn_rot = self.gu_rot.data_ptr(), self.dn_rot.data_ptr()
+        if self.gu_idx_wide is not None:
+            c.gu_idx_wide, c.dn_idx_wide = self.gu_idx_wide.data_ptr(), self.dn_idx_wide.data_ptr()
 
     # bytes per activation-code row / scale row for K columns in this pool's mode
     def code_bytes(self, k: int) -> int:

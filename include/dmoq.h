@@ -85,6 +85,11 @@ typedef struct dmoq_pool {
   /* per-forward buffers owned by the caller */
   void* act_codes;        /* gate_up-side activation codes, act_cap_rows rows (see dmoq_rotate_quant) */
   void* act_scales;
+  /* optional (1- and 2-bit pools): the same indices with every code widened to a 4-bit field,
+     (G, N, 64) bytes, made by dmoq_widen_indices.  The tensor-core GEMM looks widened codes up with
+     byte permutes instead of spreading bits; when NULL these pools run on the warp-level kernel. */
+  const uint8_t* gu_idx_wide;
+  const uint8_t* dn_idx_wide;
 } dmoq_pool_t;
 
 /* Routing tables produced by dmoq_route_build; all int32 unless noted. */
@@ -221,6 +226,13 @@ int dmoq_combine(const dmoq_route_t* route, const uint16_t* dn, int32_t hidden,
  */
 int dmoq_convert_group_first(const uint8_t* row_major, int32_t N, int32_t K, int32_t bit,
                              uint8_t* group_first, void* stream);
+
+/*
+ * Widen 1- or 2-bit codes to 4-bit fields (low field first): n_bytes packed bytes -> n_bytes*4/bit bytes.
+ * A runtime layout of this library (no reference counterpart): group-first indices (G, N, 16*bit) become
+ * (G, N, 64) for dmoq_pool_t.gu_idx_wide / dn_idx_wide.
+ */
+int dmoq_widen_indices(const uint8_t* packed, int64_t n_bytes, int32_t bit, uint8_t* wide, void* stream);
 
 #ifdef __cplusplus
 }

@@ -195,6 +195,21 @@ def test_rotate_quantize_gather_and_errors():
     assert q0.shape == (0, 256) and s0.shape == (0, 2)
 
 
+@pytest.mark.parametrize("bit", [1, 2])
+def test_widen_indices(bit):
+    """Every 1- or 2-bit code becomes one 4-bit field, low field first."""
+    g = torch.Generator().manual_seed(bit)
+    packed = torch.randint(0, 256, (3, 40, 16 * bit), dtype=torch.uint8, generator=g)
+    codes = F.unpack_nbit(packed.reshape(-1, 16 * bit), bit, 128).reshape(-1)          # one code per entry
+    want = (codes[0::2] | (codes[1::2] << 4)).to(torch.uint8).reshape(3, 40, 64)
+    src = packed.to(DEV)
+    dst = torch.zeros(3, 40, 64, dtype=torch.uint8, device=DEV)
+    lib = _lib.load()
+    _lib.check(lib.dmoq_widen_indices(_lib.ptr(src), src.numel(), bit, _lib.ptr(dst), None), "dmoq_widen_indices")
+    assert torch.equal(dst.cpu(), want)
+    assert lib.dmoq_widen_indices(_lib.ptr(src), src.numel(), 4, _lib.ptr(dst), None) == -1
+
+
 def test_group_first_relayout():
     for b in (1, 2, 4, 8):
         p = torch.randint(0, 256, (40, 3 * 16 * b), dtype=torch.uint8)
