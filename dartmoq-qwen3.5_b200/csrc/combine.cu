@@ -7,22 +7,53 @@ namespace {
 // y[t] = sum over the token's slots (then the shared row) of dn[row], fp32, fixed order.
 // Replaces final_hidden_states.index_add_(0, pool_tokens, dn)
 // (quantization/wxa16/bit_partitioned_moe.py:966), whose atomic order is not fixed.
-__global__ void combine_kernel(const int32_t* __restrict__ row_of, const uint16_t* __restrict__ dn,
-                               int T, int top_k, int has_shared, int hidden, void* y, int y_is_bf16) {
+// WEIGHTED: dn holds the plain fp16 down-projection outputs and the routing weight is applied here with the
+// reference's rounding chain fp16 -> bf16 -> (x weight in fp32) -> bf16 (module :960-965) before the sum.
+// Rows are fetched four at a time so that a thread keeps several 16-byte loads in flight.
+template <bool WEIGHTED>
+__global__ void combine_kernel(const int32_t* __restrict__ row_of, const float* __restrict__ row_weight,
+                               const uint16_t* __restrict__ dn, int T, int top_k, int has_shared, int hidden,
+                               void* y, int y_is_bf16) {
   const int chunks = hidden / 8;
   const long long total = (long long)T * chunks;
+  const int n_src = top_k + (has_shared ? 1 : 0);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const int t = (int)(i / chunks), c = (int)(i % chunks);
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const int n_src = top_k + (has_shared ? 1 : 0);
-    for (int s = 0; s < n_src; ++s) {
-      const int row = (s < top_k) ? row_of[(size_t)t * top_k + s] : row_of[(size_t)T * top_k + t];
-      if (row < 0) continue;
-      const uint4 v = *reinterpret_cast<const uint4*>(dn + (size_t)row * hidden + c * 8);
-      const uint16_t* u = reinterpret_cast<const uint16_t*>(&v);
+    for (int s0 = 0; s0 < n_src; s0 += 4) {
+      int row[4];
+      uint4 v[4];
+      float w[4];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) acc[q] += bf16_bits_to_float(u[q]);
+      for (int k = 0; k < 4; ++k) {
+        const int s = s0 + k;
+        row[k] = -1;
+        if (s < n_src) row[k] = (s < top_k) ? row_of[(size_t)t * top_k + s] : row_of[(size_t)T * top_k + t];
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        v[k] = make_uint4(0u, 0u, 0u, 0u);
+        w[k] = 0.f;
+        if (row[k] >= 0) {
+          v[k] = *reinterpret_cast<const uint4*>(dn + (size_t)row[k] * hidden + c * 8);
+          if (WEIGHTED) w[k] = row_weight[row[k]];
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (row[k] < 0) continue;
+        const uint16_t* u = reinterpret_cast<const uint16_t*>(&v[k]);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          if (WEIGHTED) {
+            const float b = __bfloat162float(__float2bfloat16_rn(__half2float(__ushort_as_half(u[q]))));
+            acc[q] += __bfloat162float(__float2bfloat16_rn(__fmul_rn(b, w[k])));
+          } else {
+            acc[q] += bf16_bits_to_float(u[q]);
+          }
+        }
+      }
     }
     __align__(16) uint16_t o[8];
 #pragma unroll
@@ -78,18 +109,34 @@ extern "C" int dmoq_widen_indices(const uint8_t* packed, int64_t n_bytes, int32_
   return dmoq_launch_status();
 }
 
-extern "C" int dmoq_combine(const dmoq_route_t* route, const uint16_t* dn, int32_t hidden,
-                            void* y, int32_t y_is_bf16, void* stream) {
+static int launch_combine(const dmoq_route_t* route, const uint16_t* dn, int32_t hidden, void* y, int32_t y_is_bf16,
+                          bool weighted, void* stream) {
   DMOQ_CHECK_ARG(route && dn && y && route->row_of);
   DMOQ_CHECK_ARG(hidden > 0 && hidden % 8 == 0);
+  DMOQ_CHECK_ARG(!weighted || route->sorted_weights);
   if (route->T == 0) return DMOQ_OK;
   const long long total = (long long)route->T * (hidden / 8);
   long long blocks = (total + 255) / 256;
   const long long cap = 8LL * dmoq_sm_count();
   if (blocks > cap) blocks = cap;
-  combine_kernel<<<(int)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      route->row_of, dn, route->T, route->top_k, route->has_shared, hidden, y, y_is_bf16);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (weighted)
+    combine_kernel<true><<<(int)blocks, 256, 0, s>>>(route->row_of, route->sorted_weights, dn, route->T, route->top_k,
+                                                     route->has_shared, hidden, y, y_is_bf16);
+  else
+    combine_kernel<false><<<(int)blocks, 256, 0, s>>>(route->row_of, nullptr, dn, route->T, route->top_k,
+                                                      route->has_shared, hidden, y, y_is_bf16);
   return dmoq_launch_status();
+}
+
+extern "C" int dmoq_combine(const dmoq_route_t* route, const uint16_t* dn, int32_t hidden,
+                            void* y, int32_t y_is_bf16, void* stream) {
+  return launch_combine(route, dn, hidden, y, y_is_bf16, false, stream);
+}
+
+extern "C" int dmoq_combine_weighted(const dmoq_route_t* route, const uint16_t* dn_f16, int32_t hidden,
+                                     void* y, int32_t y_is_bf16, void* stream) {
+  return launch_combine(route, dn_f16, hidden, y, y_is_bf16, true, stream);
 }
 
 extern "C" int dmoq_convert_group_first(const uint8_t* row_major, int32_t N, int32_t K, int32_t bit,

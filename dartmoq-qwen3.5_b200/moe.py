@@ -355,7 +355,7 @@ class _Engine:
         scale_b = max(max(p.scale_bytes(self.inter_max) for p in self.pools), 1)
         ws.dn_codes = torch.empty(max(R, 1) * code_b, **u8)
         ws.dn_scales = torch.empty(max(R, 1) * scale_b, **u8)
-        ws.dn = torch.empty(max(R, 1), self.hidden, dtype=torch.bfloat16, device=dev)
+        ws.dn = torch.empty(max(R, 1), self.hidden, dtype=torch.float16, device=dev)
         r = Route()
         r.T, r.top_k, r.E = T, self.k_v, self.E_v
         r.has_shared, r.tile_m, r.n_pools = int(self.has_shared), ws.tile_m, len(self.pools)
@@ -422,12 +422,15 @@ class _Engine:
                   "dmoq_rotate_quant_down")
             mark("rotate_quant_down:" + p.key)
             part = None if partials is None else partials.get(("down", p.key))
-            check(lib.dmoq_grouped_gemm(C.byref(ws.route), self.pool_array, i, 1, EPI_WEIGHTED, self.hidden,
+            # plain fp16 rows; the routing weight and its bf16 rounding chain are applied by the combine, which
+            # is bound by HBM and has arithmetic to spare
+            check(lib.dmoq_grouped_gemm(C.byref(ws.route), self.pool_array, i, 1, EPI_PLAIN, self.hidden,
                                         ptr(ws.dn_codes), ptr(ws.dn_scales), self.inter_max,
                                         ptr(ws.dn), self.hidden, ptr(part), s), "dmoq_grouped_gemm(down)")
-            mark("down_weighted:" + p.key)
+            mark("down:" + p.key)
         y = torch.empty_like(x)
-        check(lib.dmoq_combine(C.byref(ws.route), ptr(ws.dn), self.hidden, ptr(y), is_bf16, s), "dmoq_combine")
+        check(lib.dmoq_combine_weighted(C.byref(ws.route), ptr(ws.dn), self.hidden, ptr(y), is_bf16, s),
+              "dmoq_combine_weighted")
         mark("combine")
         return y
 

@@ -221,6 +221,15 @@ int dmoq_combine(const dmoq_route_t* route, const uint16_t* dn, int32_t hidden,
                  void* y, int32_t y_is_bf16, void* stream);
 
 /*
+ * The same combine over PLAIN fp16 down outputs: the routing weight of each row (route->sorted_weights) is
+ * applied here with the reference's rounding chain, y[t] = sum_slots bf16( bf16(fp16 dn[row]) * w[row] ), so
+ * the down GEMM can use DMOQ_EPI_PLAIN.  Bit-identical to DMOQ_EPI_WEIGHTED followed by dmoq_combine
+ * (quantization/wxa16/bit_partitioned_moe.py:960-967).
+ */
+int dmoq_combine_weighted(const dmoq_route_t* route, const uint16_t* dn_f16, int32_t hidden,
+                          void* y, int32_t y_is_bf16, void* stream);
+
+/*
  * Runtime layout conversion (N, K*bit/8) row-major bytes -> (K/128, N, 16*bit) on the device
  * (turboquant_utils/triton_kernels.py:1042).
  */

@@ -479,6 +479,29 @@ def test_small_batch_graph_replay_matches_eager(mode):
     assert rel_fro(outs[0].float().cpu().numpy(), ref) < TOL[mode]
 
 
+@pytest.mark.parametrize("mode", ["wxa16", "wxa8"])
+def test_weighted_combine_equals_weighted_epilogue(mode):
+    """Plain down rows + dmoq_combine_weighted == DMOQ_EPI_WEIGHTED rows + dmoq_combine, bit for bit."""
+    moe = _layer(mode, seed=21).to(DEV)
+    T = 333
+    x = synth.make_activations(T, 256, seed=5, device=DEV)
+    y1 = moe(x.unsqueeze(0))[0]
+    eng = moe._get_engine(torch.device(DEV))
+    ws = eng.workspace(T)
+    lib = _lib.load()
+    dn2 = torch.zeros_like(ws.dn)
+    for i, p in enumerate(eng.pools):   # the workspace still holds this forward's routing tables and activations
+        _lib.check(lib.dmoq_rotate_quant_down(C.byref(ws.route), eng.pool_array, i, _lib.ptr(ws.act), eng.inter_max,
+                                              _lib.ptr(ws.dn_codes), _lib.ptr(ws.dn_scales), eng.inter_max, None), "rq")
+        _lib.check(lib.dmoq_grouped_gemm(C.byref(ws.route), eng.pool_array, i, 1, _lib.EPI_WEIGHTED, eng.hidden,
+                                         _lib.ptr(ws.dn_codes), _lib.ptr(ws.dn_scales), eng.inter_max,
+                                         _lib.ptr(dn2), eng.hidden, None, None), "gemm")
+    y2 = torch.empty_like(y1)
+    _lib.check(lib.dmoq_combine(C.byref(ws.route), _lib.ptr(dn2), eng.hidden, _lib.ptr(y2), 1, None), "combine")
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y2)
+
+
 def test_host_streamer_matches_direct_calls():
     """Pinned host batches through the three-stream pipeline give the results of plain module calls."""
     from dartmoq_b200.host_io import HostStreamer
