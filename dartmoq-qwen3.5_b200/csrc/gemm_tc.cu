@@ -401,9 +401,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
         }
         PROF_END(5);
         PROF_BEGIN();
-#ifdef DMOQ_TC_NOMATH
-        if (xs[0] == 1.2345f) total2[0].x += __uint_as_float(v0[0] ^ v1[5]);   // timing experiment: scale math removed
-#else
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
           const float2 n2 = nrm2[4 * m];
@@ -418,7 +415,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
             total2[j * 8 + m] = fma2(t2, n2, total2[j * 8 + m]);   // (acc*xs)*norm + total, last step fused
           }
         }
-#endif
         if (MODE == DMOQ_A8 && a.partials != nullptr) {
           const int n_out = a.is_down ? a.hidden : 2 * a.inter;
 #pragma unroll
@@ -566,11 +562,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
           const int row = own_row(i), ch = own_chunk(i);
           const uint2 v = *reinterpret_cast<const uint2*>(&S.raw[s][raw_off(row) + ch * 8]);
           const uint32_t raw[2] = {v.x, v.y};
-#ifndef DMOQ_TC_NOEXPAND
           *reinterpret_cast<uint4*>(&S.b[s][swz128(row, ch)]) = expand16<BIT>(raw, lut, false);
-#else
-          if (raw[0] == 0x12345678u && raw[1] == 0x9abcdef0u) S.b[s][0] = 1;   // timing experiment: keep the loads alive
-#endif
         }
 #ifdef DMOQ_TC_PROFILE
         prof_acc[6] += clock64() - prof_r1;
