@@ -395,3 +395,98 @@ extern "C" int dmoq_route_build_static(const dmoq_route_t* route, const int64_t*
   }
   return launch_route(a, false, s);
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Router selection: fp32 softmax over the experts, the k largest probabilities in descending order (ties: lower
+// expert index first), optionally renormalised to sum 1.  One warp per token, NPL logits per lane in registers.
+namespace {
+
+template <int NPL>
+__global__ void __launch_bounds__(256) router_topk_kernel(const float* __restrict__ logits, int T, int E, int k,
+                                                          int renormalize, float* __restrict__ topk_w,
+                                                          int64_t* __restrict__ topk_idx) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_grid = gridDim.x * (blockDim.x >> 5);
+  for (int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < T; t += warps_per_grid) {
+    float v[NPL];
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {   // expert e = i * 32 + lane: coalesced reads
+      const int e = i * 32 + lane;
+      v[i] = e < E ? logits[(size_t)t * E + e] : -INFINITY;
+      m = fmaxf(m, v[i]);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      v[i] = (i * 32 + lane < E) ? expf(v[i] - m) : -1.f;   // probabilities are >= 0; -1 marks padding / taken
+      sum += fmaxf(v[i], 0.f);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+    float my_w = 0.f, top_sum = 0.f;   // lane j keeps the j-th selection
+    int my_e = 0;
+    for (int j = 0; j < k; ++j) {
+      float best = -1.f;
+      int best_e = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) {
+        if (v[i] > best) {   // strict: the lower expert index wins inside a lane
+          best = v[i];
+          best_e = i * 32 + lane;
+        }
+      }
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, d);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, d);
+        if (ob > best || (ob == best && oe < best_e)) {
+          best = ob;
+          best_e = oe;
+        }
+      }
+      const float p = __fdiv_rn(best, sum);
+      top_sum += p;
+      if (lane == j) {
+        my_w = p;
+        my_e = best_e;
+      }
+      if ((best_e & 31) == lane) {
+#pragma unroll
+        for (int i = 0; i < NPL; ++i)
+          if (i == (best_e >> 5)) v[i] = -1.f;
+      }
+    }
+    if (lane < k) {
+      topk_w[(size_t)t * k + lane] = renormalize ? __fdiv_rn(my_w, top_sum) : my_w;
+      topk_idx[(size_t)t * k + lane] = my_e;
+    }
+  }
+}
+
+template <int NPL>
+int launch_router(const float* logits, int T, int E, int k, int renorm, float* w, int64_t* idx, cudaStream_t s) {
+  int blocks = dmoq_ceil_div(T, 8);
+  const int cap = 16 * dmoq_sm_count();
+  if (blocks > cap) blocks = cap;
+  router_topk_kernel<NPL><<<blocks, 256, 0, s>>>(logits, T, E, k, renorm, w, idx);
+  return dmoq_launch_status();
+}
+
+}  // namespace
+
+extern "C" int dmoq_router_topk(const float* logits, int32_t T, int32_t E, int32_t top_k, int32_t renormalize,
+                                float* topk_w, int64_t* topk_idx, void* stream) {
+  DMOQ_CHECK_ARG(logits && topk_w && topk_idx && T >= 0);
+  DMOQ_CHECK_ARG(E > 0 && E <= 1024 && top_k > 0 && top_k <= 32 && top_k <= E);
+  if (T == 0) return DMOQ_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (E <= 32) return launch_router<1>(logits, T, E, top_k, renormalize, topk_w, topk_idx, s);
+  if (E <= 64) return launch_router<2>(logits, T, E, top_k, renormalize, topk_w, topk_idx, s);
+  if (E <= 128) return launch_router<4>(logits, T, E, top_k, renormalize, topk_w, topk_idx, s);
+  if (E <= 256) return launch_router<8>(logits, T, E, top_k, renormalize, topk_w, topk_idx, s);
+  if (E <= 512) return launch_router<16>(logits, T, E, top_k, renormalize, topk_w, topk_idx, s);
+  return launch_router<32>(logits, T, E, top_k, renormalize, topk_w, topk_idx, s);
+}

@@ -163,6 +163,19 @@ class _HostRoute:
         self.c = r
 
 
+def router_topk(logits: torch.Tensor, top_k: int, renormalize: bool = False):
+    """fp32 softmax over experts -> top-k probabilities (descending) and indices (int64), optionally renormalised:
+    the router stage of the module (quantization/wxa16/bit_partitioned_moe.py:1113-1119) as one launch."""
+    _need_cuda(logits)
+    lg = logits.to(torch.float32).contiguous()
+    T, E = lg.shape
+    w = torch.empty((T, top_k), dtype=torch.float32, device=lg.device)
+    idx = torch.empty((T, top_k), dtype=torch.int64, device=lg.device)
+    check(_lib.load().dmoq_router_topk(ptr(lg), T, E, top_k, int(renormalize), ptr(w), ptr(idx), _stream()),
+          "dmoq_router_topk")
+    return w, idx
+
+
 def _merged(mode: int, is_down: bool, a_codes: torch.Tensor, a_scales: Optional[torch.Tensor], a_stride: int,
             indices_gf: torch.Tensor, lut: torch.Tensor, norms_gf: torch.Tensor, expert_info, group_size: int,
             bit_width: int, norms_prescaled: bool, *, e0: int = 0, identity: bool = False,

@@ -618,6 +618,9 @@ class WxA16BitPartitionedGroupMoE(nn.Module):
         gate_out = self.gate(x)
         if isinstance(gate_out, tuple):
             _, topk_w, topk_idx = gate_out
+        elif gate_out.is_cuda and gate_out.shape[-1] <= 1024 and self.top_k <= 32:
+            from .kernels import router_topk
+            topk_w, topk_idx = router_topk(gate_out.reshape(-1, gate_out.shape[-1]), self.top_k)
         else:
             topk_w, topk_idx = gate_out.softmax(dim=-1).topk(self.top_k, dim=-1)
         shared_w = None

@@ -135,6 +135,15 @@ int dmoq_route_build(const dmoq_route_t* route, const int64_t* topk_idx, const f
                      const float* shared_w, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Router selection feeding dmoq_route_build: fp32 softmax of the logits (T, E), the top_k largest
+ * probabilities in descending order with their expert indices, renormalised to sum 1 when `renormalize`
+ * (the model's router: softmax -> topk [-> normalise]; the module's fallback for gates that return logits is
+ * softmax -> topk, quantization/wxa16/bit_partitioned_moe.py:1113-1119).  E <= 1024, top_k <= 32.
+ */
+int dmoq_router_topk(const float* logits, int32_t T, int32_t E, int32_t top_k, int32_t renormalize,
+                     float* topk_w, int64_t* topk_idx, void* stream);
+
+/*
  * dmoq_route_build for callers that cannot allocate device memory (no counterpart in the reference,
  * whose routing runs as torch ops that allocate freely).  Who needs it: code that runs while a stream
  * is being captured, serving loops that froze their memory pools, host frameworks that own all

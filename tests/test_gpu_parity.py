@@ -195,6 +195,21 @@ def test_rotate_quantize_gather_and_errors():
     assert q0.shape == (0, 256) and s0.shape == (0, 2)
 
 
+@pytest.mark.parametrize("T,E,k,renorm", [(1, 8, 2, True), (37, 256, 8, True), (500, 128, 4, False), (64, 1000, 32, True)])
+def test_router_topk_matches_torch(T, E, k, renorm):
+    """softmax -> top-k (-> renormalise) in one launch: same experts, weights within a few fp32 ulps of torch's."""
+    g = torch.Generator().manual_seed(T + E)
+    logits = (torch.randn(T, E, generator=g) * 3).to(DEV)
+    w, idx = K.router_topk(logits, k, renormalize=renorm)
+    pw, pidx = torch.softmax(logits, dim=-1).topk(k, dim=-1)
+    if renorm:
+        pw = pw / pw.sum(dim=-1, keepdim=True)
+    assert idx.dtype == torch.int64 and torch.equal(idx, pidx)
+    assert torch.allclose(w, pw, rtol=2e-6, atol=1e-9)
+    lib = _lib.load()
+    assert lib.dmoq_router_topk(_lib.ptr(logits), T, E, E + 1, 0, _lib.ptr(w), _lib.ptr(idx), None) == -1
+
+
 @pytest.mark.parametrize("bit", [1, 2])
 def test_widen_indices(bit):
     """Every 1- or 2-bit code becomes one 4-bit field, low field first."""
