@@ -46,27 +46,30 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], u
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// 128 x 128 fp16 matrix (row pitch `pitch` elements in global memory) -> swizzled fp16 tile.  Sixteen
-// consecutive lanes read the 256 bytes of one row.  `row_src(r)` gives the global row or -1 (zero row).
-template <typename RowSrc>
-__device__ __forceinline__ void stage_matrix(uint8_t* s16, float* s_n2, const void* base, int is_bf16, size_t pitch,
-                                             size_t col0, RowSrc row_src) {
-  const int c = threadIdx.x & 15;
+// A 128 x 128 block of 16-bit values travels in two steps: global memory -> registers (sixteen consecutive lanes
+// read the 256 bytes of one row; thread t holds 16 bytes of rows t/16 + 16j), registers -> swizzled fp16 tile.
+// The split lets the loads of the NEXT block fly while the current block is finished.
+struct XRegs {
   uint4 raw[8];
-  bool have[8];
+};
+// `row_src(r)` gives the global row or -1 (zero row).
+template <typename RowSrc>
+__device__ __forceinline__ void load_block(XRegs& xr, const void* base, size_t pitch, size_t col0, RowSrc row_src) {
+  const int c = threadIdx.x & 15;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const int r = (threadIdx.x >> 4) + 16 * j;
-    const long long src = row_src(r);
-    have[j] = src >= 0;
-    raw[j] = make_uint4(0u, 0u, 0u, 0u);
-    if (have[j]) raw[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + (size_t)src * pitch + col0 + c * 8);
+    const long long src = row_src((int)(threadIdx.x >> 4) + 16 * j);
+    xr.raw[j] = make_uint4(0u, 0u, 0u, 0u);
+    if (src >= 0) xr.raw[j] = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(base) + (size_t)src * pitch + col0 + c * 8);
   }
+}
+__device__ __forceinline__ void store_block(const XRegs& xr, uint8_t* s16, float* s_n2, int is_bf16) {
+  const int c = threadIdx.x & 15;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int r = (threadIdx.x >> 4) + 16 * j;
     __align__(16) __half h[8];
-    const uint16_t* u = reinterpret_cast<const uint16_t*>(&raw[j]);
+    const uint16_t* u = reinterpret_cast<const uint16_t*>(&xr.raw[j]);
     float ss = 0.f;
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
@@ -212,8 +215,10 @@ __device__ __forceinline__ void resolve(uint8_t* smem, const uint32_t (&mask)[2]
 }
 
 // One row block: rows [0, rows) of the staged x tile, group g.  `out_row(r)` = destination row.
-template <int MODE, typename OutRow>
-__device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows, OutRow out_row) {
+// `prefetch()` is called once, at the point where the accumulators are dead and only the fix-up chains and the
+// copy-out remain: the caller starts the global loads of its next block there.
+template <int MODE, typename OutRow, typename Prefetch>
+__device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows, OutRow out_row, Prefetch prefetch) {
   const uint8_t* x16 = smem + kOff_x16;
   const uint8_t* p16 = smem + kOff_p16;
   uint8_t* stage = smem + kOff_stage;
@@ -249,6 +254,7 @@ __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows,
       for (int nt = 0; nt < 16; ++nt)
         *reinterpret_cast<__half2*>(stage + (rbase + 8 * h) * kPitchH + (8 * nt + 2 * t4) * 2) =
             __floats2half2_rn(acc[nt][2 * h], acc[nt][2 * h + 1]);
+    prefetch();
     __syncthreads();
   } else {
     constexpr int NB = (MODE == DMOQ_FP4) ? 4 : 1;      // scale blocks per row of the group
@@ -304,10 +310,14 @@ __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows,
           const float q0 = acc[nt][2 * h] * inv_s, q1 = acc[nt][2 * h + 1] * inv_s;
           uint32_t c01;
           if (MODE == DMOQ_A8) {
-            const float r0 = rintf(q0), r1 = rintf(q1);
+            // round to nearest even by adding 1.5 * 2^23: the sum's low mantissa byte is the int8 code.  An element
+            // that is not flagged is not within t of a half, so this equals the half-away rounding of the definition;
+            // |q| < 127.5 always (the row maximum maps to 127), so no clamp is needed.
+            const float m0 = q0 + 12582912.0f, m1 = q1 + 12582912.0f;
+            const float r0 = m0 - 12582912.0f, r1 = m1 - 12582912.0f;
             mask[h] |= (fabsf(q0 - r0) > 0.5f - t) ? (1u << (2 * nt)) : 0u;
             mask[h] |= (fabsf(q1 - r1) > 0.5f - t) ? (2u << (2 * nt)) : 0u;
-            c01 = code_i8(q0) | (code_i8(q1) << 8);
+            c01 = __byte_perm(__float_as_uint(m0), __float_as_uint(m1), 0x4440);
           } else {
             const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q0 - t, q1 - t), __NV_SATFINITE, __NV_E4M3);
             const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q0 + t, q1 + t), __NV_SATFINITE, __NV_E4M3);
@@ -343,6 +353,7 @@ __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows,
       }
       if (!live[h]) mask[h] = 0;
     }
+    prefetch();
     resolve<MODE, 2>(smem, mask, rbase, t4);
   }
 
@@ -382,17 +393,17 @@ __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows,
   __syncthreads();  // tiles, tables and the staged output are rewritten by the next block
 }
 
-// x tile + row norms + cleared maxima for the next row block; ends with a block-wide barrier.
-template <typename RowSrc>
-__device__ __forceinline__ void stage_x(const RotArgs& a, uint8_t* smem, int g, RowSrc row_src) {
-  stage_matrix(smem + kOff_x16, reinterpret_cast<float*>(smem + kOff_n2), a.x, a.src_is_bf16, (size_t)a.x_stride,
-               (size_t)g * kG, row_src);
+// registers -> x tile + row norms + cleared maxima for a row block; ends with a block-wide barrier.
+__device__ __forceinline__ void stage_x(const XRegs& xr, const RotArgs& a, uint8_t* smem) {
+  store_block(xr, smem + kOff_x16, reinterpret_cast<float*>(smem + kOff_n2), a.src_is_bf16);
   reinterpret_cast<uint2*>(smem + kOff_rowmax)[threadIdx.x] = make_uint2(0u, 0u);
   __syncthreads();
 }
 
 __device__ __forceinline__ void stage_rotation(uint8_t* smem, const uint16_t* mat) {
-  stage_matrix(smem + kOff_p16, nullptr, mat, 0, kG, 0, [](int r) { return (long long)r; });
+  XRegs pr;
+  load_block(pr, mat, kG, 0, [](int r) { return (long long)r; });
+  store_block(pr, smem + kOff_p16, nullptr, 0);
 }
 
 template <int MODE>
@@ -402,11 +413,19 @@ __global__ void __launch_bounds__(kThreads, 2) rotq_mma_rows_kernel(RotArgs a) {
   const int n_rows = a.n_rows_dev ? min(*a.n_rows_dev, a.n_rows) : a.n_rows;
   const int n_blocks = (n_rows + kRows - 1) / kRows;
   if ((int)blockIdx.y >= n_blocks) return;
+  auto load = [&](XRegs& xr, int b) {
+    const int row0 = b * kRows, rows = min(kRows, n_rows - row0);
+    load_block(xr, a.x, (size_t)a.x_stride, (size_t)g * kG,
+               [&](int r) { return r < rows ? (long long)(a.src_row ? a.src_row[row0 + r] : row0 + r) : -1LL; });
+  };
+  XRegs xr;
+  load(xr, blockIdx.y);
   stage_rotation(smem, a.rot + (size_t)g * kG * kG);
   for (int b = blockIdx.y; b < n_blocks; b += gridDim.y) {
     const int row0 = b * kRows, rows = min(kRows, n_rows - row0);
-    stage_x(a, smem, g, [&](int r) { return r < rows ? (long long)(a.src_row ? a.src_row[row0 + r] : row0 + r) : -1LL; });
-    rotq_mma_block<MODE>(a, smem, g, rows, [&](int r) { return row0 + r; });
+    stage_x(xr, a, smem);
+    rotq_mma_block<MODE>(a, smem, g, rows, [&](int r) { return row0 + r; },
+                         [&]() { if (b + (int)gridDim.y < n_blocks) load(xr, b + gridDim.y); });
   }
 }
 
@@ -416,19 +435,43 @@ __global__ void __launch_bounds__(kThreads, 2) rotq_mma_tiles_kernel(RotArgs a) 
   const int g = blockIdx.x;
   const int n_tiles = a.n_tiles[a.pool];
   const DmoqTile* tiles = a.tiles + a.n_tiles[DMOQ_MAX_POOLS + a.pool];
+  auto load = [&](XRegs& xr, const DmoqTile& tile, int r0) {
+    const int row0 = tile.row0 + r0, rows = min(kRows, tile.rows - r0);
+    load_block(xr, a.x, (size_t)a.x_stride, (size_t)g * kG, [&](int r) { return r < rows ? (long long)(row0 + r) : -1LL; });
+  };
   int loaded = -1;
-  for (int t = blockIdx.y; t < n_tiles; t += gridDim.y) {
-    const DmoqTile tile = tiles[t];
+  int t = blockIdx.y;
+  if (t >= n_tiles) return;
+  DmoqTile tile = tiles[t];
+  int r0 = 0;
+  XRegs xr;
+  load(xr, tile, 0);
+  while (true) {
     const int mat = tile.rank * a.groups_per_member + g;
     if (mat != loaded) {   // every thread left the previous block through its closing barrier
       stage_rotation(smem, a.rot + (size_t)mat * kG * kG);
       loaded = mat;
     }
-    for (int r0 = 0; r0 < tile.rows; r0 += kRows) {
-      const int row0 = tile.row0 + r0, rows = min(kRows, tile.rows - r0);
-      stage_x(a, smem, g, [&](int r) { return r < rows ? (long long)(row0 + r) : -1LL; });
-      rotq_mma_block<MODE>(a, smem, g, rows, [&](int r) { return row0 + r; });
+    const int row0 = tile.row0 + r0, rows = min(kRows, tile.rows - r0);
+    // the block after this one: the next 128 rows of the tile, else the first rows of this CTA's next tile
+    int t_n = t, r0_n = r0 + kRows;
+    DmoqTile tile_n = tile;
+    if (r0_n >= tile.rows) {
+      t_n = t + gridDim.y;
+      r0_n = 0;
     }
+    const bool more = t_n < n_tiles;
+    stage_x(xr, a, smem);
+    rotq_mma_block<MODE>(a, smem, g, rows, [&](int r) { return row0 + r; }, [&]() {
+      if (more) {
+        if (t_n != t) tile_n = tiles[t_n];
+        load(xr, tile_n, r0_n);
+      }
+    });
+    if (!more) break;
+    t = t_n;
+    r0 = r0_n;
+    tile = tile_n;
   }
 }
 

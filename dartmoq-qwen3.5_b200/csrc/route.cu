@@ -47,10 +47,15 @@ __device__ void scan_and_tiles(const RouteArgs& a, int32_t* s_count /* E_tot+1 i
   // rows per expert; chunk histograms become exclusive chunk offsets
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int run = 0;
-    for (int c = 0; c < a.n_chunks; ++c) {
-      int v = a.hist[(size_t)c * E + e];
-      a.hist[(size_t)c * E + e] = run;
-      run += v;
+    for (int c0 = 0; c0 < a.n_chunks; c0 += 16) {   // sixteen independent loads in flight, then the serial prefix
+      int v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = (c0 + i < a.n_chunks) ? a.hist[(size_t)(c0 + i) * E + e] : 0;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        if (c0 + i < a.n_chunks) a.hist[(size_t)(c0 + i) * E + e] = run;
+        run += v[i];
+      }
     }
     s_count[e] = run;
   }
@@ -235,7 +240,7 @@ __global__ void route_hist_kernel(RouteArgs a) {
   for (int e = threadIdx.x; e < a.r.E; e += blockDim.x) a.hist[(size_t)blockIdx.x * a.r.E + e] = s_dyn[e];
 }
 
-__global__ void route_scan_kernel(RouteArgs a) {
+__global__ void __launch_bounds__(1024) route_scan_kernel(RouteArgs a) {
   extern __shared__ int32_t s_dyn[];
   scan_and_tiles(a, s_dyn);
 }
@@ -251,7 +256,7 @@ __global__ void route_place_kernel(RouteArgs a) {
 }
 
 // Small problems (one chunk): everything in a single block.
-__global__ void route_fused_kernel(RouteArgs a) {
+__global__ void __launch_bounds__(1024) route_fused_kernel(RouteArgs a) {
   extern __shared__ int32_t s_dyn[];  // placement tables first, then E+2 counts
   const PlaceSmem m = carve_place_smem(s_dyn, a.r.E);
   int32_t* s_count = s_dyn + (place_smem_bytes(a.r.E) + 3) / 4;

@@ -361,6 +361,30 @@ def test_module_forward_vs_oracle(mode, T):
     assert rel_fro(y.float().cpu().numpy(), ref["y"]) < TOL[mode]
 
 
+class _LogitsGate(torch.nn.Module):
+    """A gate that returns plain logits, the form the module handles with softmax -> topk itself."""
+
+    def __init__(self, n_tokens, n_experts, seed):
+        super().__init__()
+        g = torch.Generator().manual_seed(seed)
+        self.register_buffer("table", torch.randn(n_tokens, n_experts, generator=g) * 2)
+
+    def forward(self, x):
+        return self.table[:x.shape[0]]
+
+
+def test_module_with_logits_gate_uses_fused_router():
+    """Gates that return logits go through dmoq_router_topk on the GPU; same result as softmax -> topk in torch."""
+    moe = _layer("wxa8", seed=3)
+    T = 200
+    moe.gate = _LogitsGate(T, moe.num_experts, seed=8)
+    x = synth.make_activations(T, 256, seed=2)
+    tw, ti, sw = routing(moe, x)
+    ref = O.moe_forward(to_oracle_layer(moe), x, tw, ti, sw)
+    y = moe.to(DEV)(x.to(DEV).unsqueeze(0))[0]
+    assert rel_fro(y.float().cpu().numpy(), ref["y"]) < TOL["wxa8"]
+
+
 @pytest.mark.parametrize("hoist", [True, False])
 def test_a8_stages_bit_exact(hoist):
     """INT8 path, stage by stage: activation codes, stored scales and int32 group sums equal the oracle's."""
