@@ -17,7 +17,30 @@
 // rotation.py:176) is the rounded MMA value: a floating-point output, not a code.
 #include "rotq.cuh"
 
+#ifdef DMOQ_ROTQ_PROFILE
+__device__ unsigned long long g_rotq_prof[16];
+#define RP_T(i)                                                                 \
+  do {                                                                          \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {               \
+      const long long now_ = clock64();                                         \
+      atomicAdd(&g_rotq_prof[i], (unsigned long long)(now_ - rp_last));         \
+      rp_last = now_;                                                           \
+    }                                                                           \
+  } while (0)
+#define RP_START()                                                              \
+  do {                                                                          \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) rp_last = clock64(); \
+  } while (0)
+#else
+#define RP_T(i)
+#define RP_START()
+#endif
+
 namespace {
+
+#ifdef DMOQ_ROTQ_PROFILE
+__device__ long long rp_last;
+#endif
 
 constexpr int kG = DMOQ_GROUP;
 constexpr int kRows = 128;            // rows per block
@@ -116,26 +139,24 @@ __device__ __forceinline__ void chain_step(float& acc, const uint4& xv, const ui
     acc = fmaf(xf.y, pf.y, acc);
   }
 }
+// The loads of chunk c+1 are issued before the eight dependent FMAs of chunk c, so the chain runs at the FMA
+// latency instead of waiting on shared memory in every step.
 __device__ __forceinline__ float chain1(ChainSrc x, ChainSrc p) {
   float acc = 0.f;
-#pragma unroll 4
-  for (uint32_t c = 0; c < 256; c += 16)
-    chain_step(acc, *reinterpret_cast<const uint4*>(x.row + (c ^ x.sw)), *reinterpret_cast<const uint4*>(p.row + (c ^ p.sw)));
+  uint4 xv = *reinterpret_cast<const uint4*>(x.row + x.sw), pv = *reinterpret_cast<const uint4*>(p.row + p.sw);
+#pragma unroll
+  for (uint32_t c = 0; c < 256; c += 16) {
+    uint4 xn = xv, pn = pv;
+    if (c + 16 < 256) {
+      xn = *reinterpret_cast<const uint4*>(x.row + ((c + 16) ^ x.sw));
+      pn = *reinterpret_cast<const uint4*>(p.row + ((c + 16) ^ p.sw));
+    }
+    chain_step(acc, xv, pv);
+    xv = xn;
+    pv = pn;
+  }
   return acc;
 }
-__device__ __forceinline__ void chain2(ChainSrc x0, ChainSrc p0, ChainSrc x1, ChainSrc p1, float& r0, float& r1) {
-  float a0 = 0.f, a1 = 0.f;
-#pragma unroll 2
-  for (uint32_t c = 0; c < 256; c += 16) {
-    const uint4 xa = *reinterpret_cast<const uint4*>(x0.row + (c ^ x0.sw)), pa = *reinterpret_cast<const uint4*>(p0.row + (c ^ p0.sw));
-    const uint4 xb = *reinterpret_cast<const uint4*>(x1.row + (c ^ x1.sw)), pb = *reinterpret_cast<const uint4*>(p1.row + (c ^ p1.sw));
-    chain_step(a0, xa, pa);
-    chain_step(a1, xb, pb);
-  }
-  r0 = a0;
-  r1 = a1;
-}
-
 // What a thread does with the chain value of queue entry (row, col).
 //   PHASE 1: fold |v| into the exact maximum of the entry's (row, 32-column block).
 //   PHASE 2: quantise with the row's / block's scale and overwrite the staged approximate code.
@@ -196,22 +217,17 @@ __device__ __forceinline__ void resolve(uint8_t* smem, const uint32_t (&mask)[2]
       }
     }
     __syncthreads();
+    RP_T(8 + (PHASE - 1) * 3);       // scan + enqueue
     const int n = min(kQueueCap, total - q0);
-    for (int i = tid; i < n; i += 2 * kThreads) {
+    for (int i = tid; i < n; i += kThreads) {   // one chain at a time: registers stay free for the prefetched block
       const int e0 = entry[i];
-      if (i + kThreads < n) {
-        const int e1 = entry[i + kThreads];
-        float v0, v1;
-        chain2(chain_src(x16, e0 >> 8), chain_src(p16, e0 & 255), chain_src(x16, e1 >> 8), chain_src(p16, e1 & 255), v0, v1);
-        consume<MODE, PHASE>(smem, e0, v0);
-        consume<MODE, PHASE>(smem, e1, v1);
-      } else {
-        consume<MODE, PHASE>(smem, e0, chain1(chain_src(x16, e0 >> 8), chain_src(p16, e0 & 255)));
-      }
+      consume<MODE, PHASE>(smem, e0, chain1(chain_src(x16, e0 >> 8), chain_src(p16, e0 & 255)));
     }
+    RP_T(9 + (PHASE - 1) * 3);       // this thread's chains
     if (q0 + kQueueCap < total) __syncthreads();   // the queue is refilled
   }
   __syncthreads();
+  RP_T(10 + (PHASE - 1) * 3);        // waiting for the slowest warp
 }
 
 // One row block: rows [0, rows) of the staged x tile, group g.  `out_row(r)` = destination row.
@@ -227,6 +243,7 @@ __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows,
   const int mat = lane >> 3, rr = lane & 7, t4 = lane & 3;
   const int rbase = warp * 16 + (lane >> 2);
 
+  RP_T(0);   // staging (and whatever preceded this block)
   // ---- approximate rotation on the tensor cores: warp = 16 rows x 128 columns
   float acc[16][4];
 #pragma unroll
@@ -284,7 +301,9 @@ __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows,
         }
       }
     }
+    RP_T(1);   // MMA + phase-1 flags
     resolve<MODE, 1>(smem, mask, rbase, t4);
+    RP_T(2);   // phase-1 chains
 
     // ---- phase 2: approximate codes for everything, exact ones where the approximation cannot decide
     const uint32_t* rowmax = reinterpret_cast<const uint32_t*>(smem + kOff_rowmax);
@@ -353,8 +372,11 @@ __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows,
       }
       if (!live[h]) mask[h] = 0;
     }
+    RP_T(3);   // phase-2 owner part
     prefetch();
+    RP_T(6);   // prefetch issue
     resolve<MODE, 2>(smem, mask, rbase, t4);
+    RP_T(4);   // prefetch issue + phase-2 chains
   }
 
   // ---- coalesced copy-out of the staged tile
@@ -391,6 +413,7 @@ __device__ void rotq_mma_block(const RotArgs& a, uint8_t* smem, int g, int rows,
     }
   }
   __syncthreads();  // tiles, tables and the staged output are rewritten by the next block
+  RP_T(5);   // copy-out
 }
 
 // registers -> x tile + row norms + cleared maxima for a row block; ends with a block-wide barrier.
@@ -413,6 +436,7 @@ __global__ void __launch_bounds__(kThreads, 2) rotq_mma_rows_kernel(RotArgs a) {
   const int n_rows = a.n_rows_dev ? min(*a.n_rows_dev, a.n_rows) : a.n_rows;
   const int n_blocks = (n_rows + kRows - 1) / kRows;
   if ((int)blockIdx.y >= n_blocks) return;
+  RP_START();
   auto load = [&](XRegs& xr, int b) {
     const int row0 = b * kRows, rows = min(kRows, n_rows - row0);
     load_block(xr, a.x, (size_t)a.x_stride, (size_t)g * kG,
@@ -442,6 +466,7 @@ __global__ void __launch_bounds__(kThreads, 2) rotq_mma_tiles_kernel(RotArgs a) 
   int loaded = -1;
   int t = blockIdx.y;
   if (t >= n_tiles) return;
+  RP_START();
   DmoqTile tile = tiles[t];
   int r0 = 0;
   XRegs xr;
@@ -461,12 +486,10 @@ __global__ void __launch_bounds__(kThreads, 2) rotq_mma_tiles_kernel(RotArgs a) 
       r0_n = 0;
     }
     const bool more = t_n < n_tiles;
+    if (more && t_n != t) tile_n = tiles[t_n];   // fetched now, used by the prefetch below: no dependent-load stall there
     stage_x(xr, a, smem);
     rotq_mma_block<MODE>(a, smem, g, rows, [&](int r) { return row0 + r; }, [&]() {
-      if (more) {
-        if (t_n != t) tile_n = tiles[t_n];
-        load(xr, tile_n, r0_n);
-      }
+      if (more) load(xr, tile_n, r0_n);
     });
     if (!more) break;
     t = t_n;
@@ -529,3 +552,14 @@ int dmoq_rotq_mma_tiles(int mode, const RotArgs& a, int tile_cap, cudaStream_t s
     default: return DMOQ_EINVAL;
   }
 }
+
+#ifdef DMOQ_ROTQ_PROFILE
+extern "C" int dmoq_rotq_profile(unsigned long long* out16, int reset) {
+  if (cudaMemcpyFromSymbol(out16, g_rotq_prof, sizeof(unsigned long long) * 16) != cudaSuccess) return DMOQ_EDEVICE;
+  if (reset) {
+    unsigned long long z[16] = {0};
+    if (cudaMemcpyToSymbol(g_rotq_prof, z, sizeof(z)) != cudaSuccess) return DMOQ_EDEVICE;
+  }
+  return DMOQ_OK;
+}
+#endif
