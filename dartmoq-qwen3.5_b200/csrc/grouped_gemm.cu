@@ -83,6 +83,8 @@ struct Mma<DMOQ_A16> : MmaF16 {};
 template <>
 struct Mma<DMOQ_FP4> : MmaF16 {};
 
+constexpr int kAStages = 3;   // activation operand tiles in flight (copies are issued two groups ahead)
+
 template <int MODE>
 struct Traits {
   static constexpr int ES = (MODE == DMOQ_A8 || MODE == DMOQ_FP8) ? 1 : 2;  // operand element bytes in smem
@@ -115,9 +117,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
   constexpr int KSTEPS_BLK = T::SG * ES / 32;
 
   extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t* s_a = smem;                                   // 2 x TILEA
-  uint8_t* s_b = smem + 2 * TILEA;                       // 2 x TILEB
-  float* s_norm = reinterpret_cast<float*>(smem + 2 * TILEA + 2 * TILEB);   // 2 x 128
+  uint8_t* s_a = smem;                                   // kAStages x TILEA (activation copies run two groups ahead)
+  uint8_t* s_b = smem + kAStages * TILEA;                // 2 x TILEB
+  float* s_norm = reinterpret_cast<float*>(smem + kAStages * TILEA + 2 * TILEB);   // 2 x 128
   float* s_rs = s_norm + 2 * kBN;                                    // 2 x 128 x 4
   int32_t* s_arow = reinterpret_cast<int32_t*>(s_rs + 2 * kBM * 4);  // 128
   uint8_t* s_blut = reinterpret_cast<uint8_t*>(s_arow + kBM);        // 256 x EB
@@ -172,16 +174,18 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
     const int bj = tid >> 2, bq = tid & 3;
     const int brow = wrow(bj);
 
-    uint32_t raw_b[PB / 4 > 0 ? PB / 4 : 1];
-    uint4 raw_a4 = make_uint4(0, 0, 0, 0);  // FP4 activation nibbles (32 elements)
+    // Everything a thread fetches from global memory for one group and keeps in registers until the group's
+    // operand tile is built: packed weight indices, FP4 activation nibbles, the row scale or column norm it
+    // stages.  Two groups are in flight (loaded two steps ahead of their use), so the loads have a whole
+    // compute step to land; at small row counts this is what the kernel's time is made of.
+    struct GroupRegs {
+      uint32_t raw_b[PB / 4 > 0 ? PB / 4 : 1];
+      uint4 raw_a4;    // FP4 activation nibbles (32 elements)
+      uint32_t sc;     // tid < kBM: activation scale bits of row tid; kBM <= tid < kBM + kBN: norm bits of a column
+    };
 
-    auto issue_loads = [&](int g, int buf) {
-      // activation codes
-      if (MODE == DMOQ_FP4) {
-        const int ar = bj < kBM ? s_arow[bj] : -1;
-        if (ar >= 0) raw_a4 = *reinterpret_cast<const uint4*>(a.a_codes + (size_t)ar * (a.a_stride / 2) + g * (kG / 2) + bq * 16);
-        else raw_a4 = make_uint4(0, 0, 0, 0);
-      } else {
+    auto issue_a = [&](int g, int buf) {   // activation codes: asynchronous copies into the operand tile
+      if (MODE != DMOQ_FP4) {
         constexpr int CH = ROWB / 16;  // chunks per row
         for (int c = tid; c < kBM * CH; c += kThreads) {
           const int r = c / CH, ch = c % CH;
@@ -191,43 +195,46 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
         }
       }
       cp_async_commit();
+    };
+
+    auto load_group = [&](int g, GroupRegs& w) {
+      w.raw_a4 = make_uint4(0, 0, 0, 0);
+      if (MODE == DMOQ_FP4) {
+        const int ar = bj < kBM ? s_arow[bj] : -1;
+        if (ar >= 0) w.raw_a4 = *reinterpret_cast<const uint4*>(a.a_codes + (size_t)ar * (a.a_stride / 2) + g * (kG / 2) + bq * 16);
+      }
       // packed weight indices for this thread's 32 elements
       const uint8_t* wp = a.idx + ((size_t)(gg0 + g) * n_total + brow) * BPG + bq * PB;
-      if (PB == 4) raw_b[0] = *reinterpret_cast<const uint32_t*>(wp);
-      else if (PB == 8) { uint2 v = *reinterpret_cast<const uint2*>(wp); raw_b[0] = v.x; raw_b[1] = v.y; }
+      if (PB == 4) w.raw_b[0] = *reinterpret_cast<const uint32_t*>(wp);
+      else if (PB == 8) { uint2 v = *reinterpret_cast<const uint2*>(wp); w.raw_b[0] = v.x; w.raw_b[1] = v.y; }
       else {
 #pragma unroll
         for (int q = 0; q < PB / 16; ++q) {
           uint4 v = *reinterpret_cast<const uint4*>(wp + q * 16);
-          raw_b[q * 4 + 0] = v.x; raw_b[q * 4 + 1] = v.y; raw_b[q * 4 + 2] = v.z; raw_b[q * 4 + 3] = v.w;
+          w.raw_b[q * 4 + 0] = v.x; w.raw_b[q * 4 + 1] = v.y; w.raw_b[q * 4 + 2] = v.z; w.raw_b[q * 4 + 3] = v.w;
         }
       }
       // scales
+      w.sc = 0;
       if (tid < kBM) {
         const int ar = s_arow[tid];
-        float* rs = s_rs + (buf * kBM + tid) * 4;
-        if (MODE == DMOQ_A8 || MODE == DMOQ_FP8) {
-          rs[0] = ar >= 0 ? __half2float(reinterpret_cast<const __half*>(a.a_scales)[(size_t)ar * (a.a_stride / kG) + g]) : 0.f;
-        } else if (MODE == DMOQ_FP4) {
-          uint32_t e4 = ar >= 0 ? *reinterpret_cast<const uint32_t*>(a.a_scales + (size_t)ar * (a.a_stride / 32) + g * 4) : 0u;
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            rs[q] = ar >= 0 ? ldexpf(1.0f, (int)((e4 >> (8 * q)) & 255) - 127 + a.e0) : 0.f;
-        } else {
-          rs[0] = 1.f;
+        if (ar >= 0) {
+          if (MODE == DMOQ_A8 || MODE == DMOQ_FP8)
+            w.sc = reinterpret_cast<const uint16_t*>(a.a_scales)[(size_t)ar * (a.a_stride / kG) + g];
+          else if (MODE == DMOQ_FP4)
+            w.sc = *reinterpret_cast<const uint32_t*>(a.a_scales + (size_t)ar * (a.a_stride / 32) + g * 4);
         }
       } else if (tid < kBM + kBN) {
-        const int j = tid - kBM;
-        s_norm[buf * kBN + j] = __half2float(reinterpret_cast<const __half*>(a.norm)[(size_t)(gg0 + g) * n_total + wrow(j)]);
+        w.sc = reinterpret_cast<const uint16_t*>(a.norm)[(size_t)(gg0 + g) * n_total + wrow(tid - kBM)];
       }
     };
 
-    auto expand_to_smem = [&](int buf) {
+    auto expand_to_smem = [&](int buf, int abuf, const GroupRegs& w) {
       // weights: PB packed bytes -> 32 elements -> 2*ES chunks of 16 bytes
       __align__(16) uint8_t ob[32 * ES];
 #pragma unroll
       for (int i = 0; i < PB; ++i) {
-        const uint32_t byte = (raw_b[i >> 2] >> (8 * (i & 3))) & 255u;
+        const uint32_t byte = (w.raw_b[i >> 2] >> (8 * (i & 3))) & 255u;
         const uint8_t* e = s_blut + byte * EB;
         if (EB >= 4) {
 #pragma unroll
@@ -244,14 +251,30 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
         *reinterpret_cast<uint4*>(s_b + buf * TILEB + swz<ROWB>(bj, bq * 2 * ES + c)) = reinterpret_cast<const uint4*>(ob)[c];
       if (MODE == DMOQ_FP4 && bj < kBM) {
         __align__(16) uint16_t oa[32];
-        const uint32_t words[4] = {raw_a4.x, raw_a4.y, raw_a4.z, raw_a4.w};
+        const uint32_t words[4] = {w.raw_a4.x, w.raw_a4.y, w.raw_a4.z, w.raw_a4.w};
 #pragma unroll
         for (int i = 0; i < 32; ++i) oa[i] = kE2M1Half[(words[i >> 3] >> (4 * (i & 7))) & 15];
 #pragma unroll
         for (int c = 0; c < 4; ++c)
-          *reinterpret_cast<uint4*>(s_a + buf * TILEA + swz<ROWB>(bj, bq * 4 + c)) = reinterpret_cast<const uint4*>(oa)[c];
+          *reinterpret_cast<uint4*>(s_a + abuf * TILEA + swz<ROWB>(bj, bq * 4 + c)) = reinterpret_cast<const uint4*>(oa)[c];
+      }
+      if (tid < kBM) {
+        const bool live = s_arow[tid] >= 0;
+        float* rs = s_rs + (buf * kBM + tid) * 4;
+        if (MODE == DMOQ_A8 || MODE == DMOQ_FP8) {
+          rs[0] = live ? __half2float(__ushort_as_half((uint16_t)w.sc)) : 0.f;
+        } else if (MODE == DMOQ_FP4) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            rs[q] = live ? ldexpf(1.0f, (int)((w.sc >> (8 * q)) & 255) - 127 + a.e0) : 0.f;
+        } else {
+          rs[0] = 1.f;
+        }
+      } else if (tid < kBM + kBN) {
+        s_norm[buf * kBN + (tid - kBM)] = __half2float(__ushort_as_half((uint16_t)w.sc));
       }
     };
+
 
     float total[MT][NT][4];
 #pragma unroll
@@ -261,16 +284,27 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) total[i][j][q] = 0.f;
 
-    issue_loads(0, 0);
-    expand_to_smem(0);
-    cp_async_wait<0>();
+    GroupRegs w_cur, w_next;   // w_next: the group built during this step; w_ahead (below): the one after
+    issue_a(0, 0);
+    if (G > 1) issue_a(1, 1); else cp_async_commit();   // one commit group per step keeps the wait counts uniform
+    load_group(0, w_cur);
+    if (G > 1) load_group(1, w_next);
+    expand_to_smem(0, 0, w_cur);
+    cp_async_wait<1>();   // group 0's activation tile has landed; group 1's may still be in flight
     __syncthreads();
 
     for (int g = 0; g < G; ++g) {
       const int buf = g & 1;
-      if (g + 1 < G) issue_loads(g + 1, buf ^ 1);
+      const int abuf = g % kAStages;
+      GroupRegs w_ahead;
+      if (g + 2 < G) {
+        issue_a(g + 2, (g + 2) % kAStages);
+        load_group(g + 2, w_ahead);
+      } else {
+        cp_async_commit();
+      }
 
-      const uint32_t a_base = smem_u32(s_a + buf * TILEA);
+      const uint32_t a_base = smem_u32(s_a + abuf * TILEA);
       const uint32_t b_base = smem_u32(s_b + buf * TILEB);
       const int mat = lane >> 3, rr = lane & 7;
 #pragma unroll
@@ -324,10 +358,12 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
         }
       }
 
-      if (g + 1 < G) expand_to_smem(buf ^ 1);
-      cp_async_wait<0>();
+      if (g + 1 < G) expand_to_smem(buf ^ 1, (g + 1) % kAStages, w_next);
+      cp_async_wait<1>();   // the next group's activation tile has landed
       __syncthreads();
+      if (g + 2 < G) w_next = w_ahead;
     }
+    cp_async_wait<0>();
 
     // ---- epilogue through shared memory (operand buffers are free now)
     if (EPI == DMOQ_EPI_SILU) {
@@ -409,7 +445,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
 
 template <int MODE, int BM>
 constexpr size_t smem_bytes(int bit) {
-  return 2 * (size_t)Traits<MODE>::TILEB + 2 * (size_t)BM * Traits<MODE>::ROWB + (2 * kBN + 2 * BM * 4) * sizeof(float) +
+  return 2 * (size_t)Traits<MODE>::TILEB + kAStages * (size_t)BM * Traits<MODE>::ROWB + (2 * kBN + 2 * BM * 4) * sizeof(float) +
          BM * sizeof(int32_t) +
          256 * (size_t)(8 / bit) * Traits<MODE>::ES + 128;
 }
