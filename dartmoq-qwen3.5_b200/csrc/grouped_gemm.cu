@@ -146,6 +146,17 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
     }
   }
 
+  // the first four 16-bit codewords in two registers (1- and 2-bit codebooks in the 16-bit operand modes)
+  uint32_t lut_r0 = 0, lut_r1 = 0;
+  if (ES == 2 && BIT <= 2) {
+    uint32_t h[4] = {0, 0, 0, 0};
+    for (int i = 0; i < (1 << BIT); ++i)
+      h[i] = (MODE == DMOQ_FP4) ? kE2M1Half[reinterpret_cast<const uint8_t*>(a.lut)[i] & 15]
+                                : reinterpret_cast<const uint16_t*>(a.lut)[i];
+    lut_r0 = h[0] | (h[1] << 16);
+    lut_r1 = h[2] | (h[3] << 16);
+  }
+
   const int n_tiles = a.n_tiles[a.pool];
   const DmoqTile* tiles = a.tiles + a.n_tiles[DMOQ_MAX_POOLS + a.pool];
   const int NB = a.is_down ? a.hidden / kBN : a.inter / (kBN / 2);
@@ -232,6 +243,31 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(GemmArgs a) {
     auto expand_to_smem = [&](int buf, int abuf, const GroupRegs& w) {
       // weights: PB packed bytes -> 32 elements -> 2*ES chunks of 16 bytes
       __align__(16) uint8_t ob[32 * ES];
+      if (ES == 2 && BIT <= 2) {
+        // 16-bit codewords of a 1- or 2-bit codebook fit two registers: look them up with byte permutes instead
+        // of the shared-memory table (at small row counts that table's bank conflicts are what the kernel waits on).
+        // Codes of one packed byte -> one code per byte -> selector nibbles (2c, 2c+1) -> two codewords per permute.
+        uint32_t* ow = reinterpret_cast<uint32_t*>(ob);
+#pragma unroll
+        for (int i = 0; i < PB; ++i) {
+          const uint32_t B = (w.raw_b[i >> 2] >> (8 * (i & 3))) & 255u;
+          if (BIT == 2) {
+            const uint32_t t = (B | (B << 6) | (B << 12) | (B << 18)) & 0x03030303u;
+            const uint32_t sel = t * 34u + 0x10101010u;
+            ow[2 * i + 0] = __byte_perm(lut_r0, lut_r1, sel);
+            ow[2 * i + 1] = __byte_perm(lut_r0, lut_r1, sel >> 16);
+          } else {
+            const uint32_t t0 = (B | (B << 7) | (B << 14) | (B << 21)) & 0x01010101u;
+            const uint32_t Bh = B >> 4;
+            const uint32_t t1 = (Bh | (Bh << 7) | (Bh << 14) | (Bh << 21)) & 0x01010101u;
+            const uint32_t s0 = t0 * 34u + 0x10101010u, s1 = t1 * 34u + 0x10101010u;
+            ow[4 * i + 0] = __byte_perm(lut_r0, lut_r1, s0);
+            ow[4 * i + 1] = __byte_perm(lut_r0, lut_r1, s0 >> 16);
+            ow[4 * i + 2] = __byte_perm(lut_r0, lut_r1, s1);
+            ow[4 * i + 3] = __byte_perm(lut_r0, lut_r1, s1 >> 16);
+          }
+        }
+      } else
 #pragma unroll
       for (int i = 0; i < PB; ++i) {
         const uint32_t byte = (w.raw_b[i >> 2] >> (8 * (i & 3))) & 255u;

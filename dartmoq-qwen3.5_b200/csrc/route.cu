@@ -41,7 +41,6 @@ __device__ void scan_and_tiles(const RouteArgs& a, int32_t* s_count /* E_tot+1 i
   const int E = a.r.E;
   const int E_tot = E + a.r.has_shared;
   const int P = a.r.n_pools;
-  __shared__ int32_t s_tile_base[DMOQ_MAX_POOLS];
   __shared__ int8_t s_pool[4100];   // pool of each expert, staged once: the serial scan below must not wait on HBM
 
   // rows per expert; chunk histograms become exclusive chunk offsets
@@ -66,47 +65,87 @@ __device__ void scan_and_tiles(const RouteArgs& a, int32_t* s_count /* E_tot+1 i
   if (threadIdx.x == 0 && a.r.has_shared) s_count[E] = a.r.T;
   __syncthreads();
 
-  if (threadIdx.x == 0) {
-    int32_t pool_rows[DMOQ_MAX_POOLS], pool_tiles[DMOQ_MAX_POOLS];
-    for (int p = 0; p < DMOQ_MAX_POOLS; ++p) pool_rows[p] = pool_tiles[p] = 0;
-    int run = 0;
-    for (int e = 0; e < E_tot; ++e) {
-      const int n = s_count[e];
-      a.r.expert_rows[e] = run;
-      run += n;
-      const int p = s_pool[e];
-      if (p >= 0) {
-        a.pool_row0[e] = pool_rows[p];
-        pool_rows[p] += n;
-        pool_tiles[p] += (n + a.r.tile_m - 1) / a.r.tile_m;
-      } else {
-        a.pool_row0[e] = 0;
+  // Prefix sums over the experts by warp 0: every lane owns a contiguous run of experts, sums its run, the
+  // warp scans the 1 + 2*pools partial sums with shuffles, then every lane walks its run again with its bases.
+  __shared__ int32_t s_slot[4100];   // first tile slot of each expert
+  __shared__ int32_t s_row0[4100];   // first row of each expert
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    const int per = (E_tot + 31) / 32;
+    const int e0 = min(lane * per, E_tot), e1 = min(e0 + per, E_tot);
+    int rows_all = 0, rows_p[DMOQ_MAX_POOLS], tiles_p[DMOQ_MAX_POOLS];
+#pragma unroll
+    for (int p = 0; p < DMOQ_MAX_POOLS; ++p) rows_p[p] = tiles_p[p] = 0;
+    for (int e = e0; e < e1; ++e) {
+      const int n = s_count[e], pl = s_pool[e];
+      const int nt = (n + a.r.tile_m - 1) / a.r.tile_m;
+      rows_all += n;
+#pragma unroll
+      for (int p = 0; p < DMOQ_MAX_POOLS; ++p) {
+        rows_p[p] += (pl == p) ? n : 0;
+        tiles_p[p] += (pl == p) ? nt : 0;
       }
     }
-    a.r.expert_rows[E_tot] = run;
-    int tb = 0;
+    auto excl_scan = [&](int v, int& total) {   // exclusive prefix over the lanes, total in every lane
+      int inc = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += o;
+      }
+      total = __shfl_sync(0xffffffffu, inc, 31);
+      return inc - v;
+    };
+    int tot_all;
+    int run = excl_scan(rows_all, tot_all);
+    int prow[DMOQ_MAX_POOLS], pslot[DMOQ_MAX_POOLS], tot_rows[DMOQ_MAX_POOLS], tot_tiles[DMOQ_MAX_POOLS];
+#pragma unroll
     for (int p = 0; p < DMOQ_MAX_POOLS; ++p) {
-      s_tile_base[p] = tb;
-      a.r.pool_rows[p] = pool_rows[p];
-      a.r.n_tiles[p] = pool_tiles[p];
-      a.r.n_tiles[DMOQ_MAX_POOLS + p] = tb;
-      tb += pool_tiles[p];
+      prow[p] = excl_scan(rows_p[p], tot_rows[p]);
+      pslot[p] = excl_scan(tiles_p[p], tot_tiles[p]);
     }
+    int tb = 0;   // pool p's tiles start after all tiles of the pools before it
+#pragma unroll
+    for (int p = 0; p < DMOQ_MAX_POOLS; ++p) {
+      pslot[p] += tb;
+      if (lane == 0) {
+        a.r.pool_rows[p] = tot_rows[p];
+        a.r.n_tiles[p] = tot_tiles[p];
+        a.r.n_tiles[DMOQ_MAX_POOLS + p] = tb;
+      }
+      tb += tot_tiles[p];
+    }
+    for (int e = e0; e < e1; ++e) {
+      const int n = s_count[e], pl = s_pool[e];
+      const int nt = (n + a.r.tile_m - 1) / a.r.tile_m;
+      a.r.expert_rows[e] = run;
+      s_row0[e] = run;
+      run += n;
+      int my_prow = 0, my_slot = 0;
+#pragma unroll
+      for (int p = 0; p < DMOQ_MAX_POOLS; ++p) {
+        if (pl == p) {
+          my_prow = prow[p];
+          my_slot = pslot[p];
+          prow[p] += n;
+          pslot[p] += nt;
+        }
+      }
+      a.pool_row0[e] = my_prow;
+      s_slot[e] = my_slot;
+    }
+    if (lane == 31) a.r.expert_rows[E_tot] = tot_all;
   }
   __syncthreads();
 
-  // tile lists: pool p's tiles are contiguous from s_tile_base[p], experts in index order.
-  // Each thread walks the experts before its own to find its first tile slot and first row.
+  // tile lists: pool p's tiles are contiguous from its base, experts in index order
   for (int e = threadIdx.x; e < E_tot; e += blockDim.x) {
     const int p = s_pool[e];
     if (p < 0) continue;
     const int n = s_count[e];
     if (n == 0) continue;
-    int slot = s_tile_base[p], row0 = 0;
-    for (int q = 0; q < e; ++q) {
-      row0 += s_count[q];
-      if (s_pool[q] == p) slot += (s_count[q] + a.r.tile_m - 1) / a.r.tile_m;
-    }
+    int slot = s_slot[e];
+    const int row0 = s_row0[e];
     const int rank = a.r.expert_rank[e];
     for (int m = 0; m < n; m += a.r.tile_m, ++slot) {
       if (slot >= a.r.tile_cap) break;
@@ -394,7 +433,6 @@ extern "C" int dmoq_route_build_static(const dmoq_route_t* route, const int64_t*
   a.hist = scratch;
   a.pool_row0 = a.hist + (size_t)a.n_chunks * r.E;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const size_t e_bytes = (size_t)r.E * sizeof(int32_t);
   if (a.n_chunks == 1 && (!r.has_shared || r.T <= 4 * kChunk)) {
     return launch_route(a, true, s);
   }
