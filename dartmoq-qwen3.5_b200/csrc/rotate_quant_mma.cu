@@ -508,7 +508,9 @@ int launch_rows(const RotArgs& a, cudaStream_t s) {
   }
   const int G = a.K / kG;
   const int n_blocks = dmoq_ceil_div(a.n_rows, kRows);
-  int gy = dmoq_ceil_div(2 * dmoq_sm_count(), G);
+  // two blocks are resident per SM: the grid must not exceed those slots, or the blocks left over run alone
+  // after the others have finished their whole share of row blocks
+  int gy = (2 * dmoq_sm_count()) / G;
   if (gy > n_blocks) gy = n_blocks;
   if (gy < 1) gy = 1;
   rotq_mma_rows_kernel<MODE><<<dim3(G, gy), kThreads, kSmem, s>>>(a);
@@ -524,7 +526,9 @@ int launch_tiles(const RotArgs& a, int tile_cap, cudaStream_t s) {
     configured = true;
   }
   const int G = a.K / kG;
-  int gy = dmoq_ceil_div(2 * dmoq_sm_count(), G);
+  // two blocks are resident per SM: the grid must not exceed those slots, or the blocks left over run alone
+  // after the others have finished their whole share of row blocks
+  int gy = (2 * dmoq_sm_count()) / G;
   if (gy > tile_cap) gy = tile_cap;
   if (gy < 1) gy = 1;
   rotq_mma_tiles_kernel<MODE><<<dim3(G, gy), kThreads, kSmem, s>>>(a);
