@@ -27,7 +27,7 @@ class DispatchPlan:
         flat_e = topk_idx.reshape(-1)
         dest = torch.div(flat_e, experts_per_rank, rounding_mode="floor")
         # stable order: by destination rank, then by flat (token, slot) index -> deterministic
-        self.order = torch.sort(dest * (T * k) + torch.arange(T * k, device=dest.device))[1]
+        self.order = torch.sort(dest, stable=True)[1]
         self.send_counts = torch.bincount(dest, minlength=world)
         self.token = torch.div(self.order, k, rounding_mode="floor")
         self.local_expert = flat_e[self.order] - dest[self.order] * experts_per_rank
@@ -51,6 +51,33 @@ def all_to_all_rows(rows: torch.Tensor, send: list, recv: list, group=None) -> t
     return out
 
 
+def _sum_slots_torch(back: torch.Tensor, inverse: torch.Tensor, T: int, k: int, dtype) -> torch.Tensor:
+    """y[t] = sum over the token's k rows, fp32, slot order (device-agnostic form)."""
+    per_pair = back[inverse].reshape(T, k, back.shape[1]).float()
+    y = per_pair[:, 0]
+    for s in range(1, k):
+        y = y + per_pair[:, s]
+    return y.to(dtype)
+
+
+def _sum_slots_cuda(back: torch.Tensor, inverse: torch.Tensor, T: int, k: int, dtype) -> torch.Tensor:
+    """The same sum through the library's deterministic combine kernel (one pass over the rows)."""
+    import ctypes as C
+    from . import _lib
+    if back.dtype != torch.bfloat16 or dtype not in (torch.bfloat16, torch.float16):
+        return _sum_slots_torch(back, inverse, T, k, dtype)
+    row_of = inverse.to(torch.int32).contiguous()
+    rows = back.contiguous()
+    y = torch.empty((T, rows.shape[1]), dtype=dtype, device=rows.device)
+    r = _lib.Route()
+    r.T, r.top_k, r.has_shared = T, k, 0
+    r.row_of = row_of.data_ptr()
+    _lib.check(_lib.load().dmoq_combine(C.byref(r), _lib.ptr(rows), rows.shape[1], _lib.ptr(y),
+                                        int(dtype == torch.bfloat16),
+                                        C.c_void_p(torch.cuda.current_stream().cuda_stream)), "dmoq_combine")
+    return y
+
+
 def ep_forward(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, experts_per_rank: int,
                local_compute: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
                group=None) -> torch.Tensor:
@@ -67,11 +94,10 @@ def ep_forward(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, ex
     out_rows = local_compute(rows, meta[:, 0].to(torch.int64), meta[:, 1])
     back = all_to_all_rows(out_rows, recv, send, group)
     # back[i] answers send row i; put the rows in (token, slot) order and add the k slots in slot order
-    per_pair = back[plan.inverse()].reshape(plan.T, plan.k, x.shape[1]).float()
-    y = per_pair[:, 0]
-    for s in range(1, plan.k):
-        y = y + per_pair[:, s]
-    return y.to(x.dtype)
+    if plan.T == 0:
+        return x.new_zeros(x.shape)
+    sum_slots = _sum_slots_cuda if back.is_cuda else _sum_slots_torch
+    return sum_slots(back, plan.inverse(), plan.T, plan.k, x.dtype)
 
 
 class ExpertParallelMoE(torch.nn.Module):
