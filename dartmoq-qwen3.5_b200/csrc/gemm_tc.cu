@@ -171,6 +171,14 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
       : "memory");
 }
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+      : "memory");
+}
 __device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                           uint32_t accumulate) {
   asm volatile(
@@ -265,6 +273,17 @@ __device__ __forceinline__ uint4 expand16(const uint32_t* raw, const Lut& lut, b
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// Eight widened codes (one 32-bit word of 4-bit fields) -> eight fp16 codewords (16 bytes) of a codebook with at
+// most four entries held in two registers: code c selects bytes (2c, 2c+1).
+__device__ __forceinline__ uint4 expand8_f16(uint32_t w, uint32_t lut0, uint32_t lut1) {
+  const uint32_t sl = (w & 0x0F0F0F0Fu) * 34u + 0x10101010u;          // selector bytes of codes 0, 2, 4, 6
+  const uint32_t sh = ((w >> 4) & 0x0F0F0F0Fu) * 34u + 0x10101010u;   // ... of codes 1, 3, 5, 7
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) o[j] = prmt(lut0, lut1, prmt(sl, sh, (uint32_t)(j | ((4 + j) << 4))));
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 struct Smem {
   // operand ring, 1024-byte aligned tiles
   uint8_t a[kStages][kTileB];
@@ -290,6 +309,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   volatile int* abort_flag = &S.abort_flag;
   constexpr int BPG = (BIT <= 2) ? 64 : 16 * BIT;    // index bytes per row per group (1/2-bit codes come widened to 4 bits)
+  // fp16 operands: a 128-byte operand row holds 64 columns, so a 128-wide group takes two operand steps
+  constexpr int SUB = (MODE == DMOQ_A16) ? 2 : 1;
+  constexpr int ES = (MODE == DMOQ_A16) ? 2 : 1;
   constexpr int kMmaWarp = kEpiWarps + kProdWarps;
 
   if (tid == 0) {
@@ -387,7 +409,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
         tc_ld16x256(taddr + (16u << 16), v1);
         float xs[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) xs[j] = S.sc_xs[slot][row_b + 8 * j];
+        for (int j = 0; j < 4; ++j) xs[j] = (MODE == DMOQ_A16) ? 1.f : S.sc_xs[slot][row_b + 8 * j];
         float off[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) off[j] = (MODE == DMOQ_A8) ? -kMagicFloat * xs[j] : 0.f;
@@ -411,7 +433,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
             const float2 f = make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
             // INT8: (acc_biased - M) * xs in one fma with the exact constant -M*xs (2 x 11 significant bits);
             // e4m3: acc * xs (adding +0 changes nothing: the product is never -0 unless acc is, and then total decides)
-            const float2 t2 = fma2(f, make_float2(xs[j], xs[j]), make_float2(off[j], off[j]));
+            // fp16 operands: no row scale, acc * norm + total
+            const float2 t2 = (MODE == DMOQ_A16) ? f : fma2(f, make_float2(xs[j], xs[j]), make_float2(off[j], off[j]));
             total2[j * 8 + m] = fma2(t2, n2, total2[j * 8 + m]);   // (acc*xs)*norm + total, last step fused
           }
         }
@@ -523,7 +546,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
     Lut lut;
 #pragma unroll
     for (int q = 0; q < 4; ++q) lut.w[q] = 0;
-    if (!(BIT == 8)) {
+    if (MODE == DMOQ_A16) {        // up to four fp16 codewords in two registers
+      for (int i = 0; i < (1 << BIT) && i < 4; ++i)
+        lut.w[i >> 1] |= (uint32_t)reinterpret_cast<const uint16_t*>(a.lut)[i] << (16 * (i & 1));
+    } else if (!(BIT == 8)) {
       for (int i = 0; i < (1 << BIT); ++i) lut.w[i >> 2] |= (uint32_t)a.lut[i] << (8 * (i & 3));
     }
     // chunk ownership: kCPT (row, 16-byte chunk) pairs per thread and stage, chosen so that a warp's
@@ -560,9 +586,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
 #pragma unroll
         for (int i = 0; i < kCPT; ++i) {
           const int row = own_row(i), ch = own_chunk(i);
-          const uint2 v = *reinterpret_cast<const uint2*>(&S.raw[s][raw_off(row) + ch * 8]);
-          const uint32_t raw[2] = {v.x, v.y};
-          *reinterpret_cast<uint4*>(&S.b[s][swz128(row, ch)]) = expand16<BIT>(raw, lut, false);
+          if (MODE == DMOQ_A16) {   // eight fp16 codewords per chunk: this step covers half hh of the group's columns
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(&S.raw[s][raw_off(row) + (j % SUB) * 32 + ch * 4]);
+            *reinterpret_cast<uint4*>(&S.b[s][swz128(row, ch)]) = expand8_f16(w, lut.w[0], lut.w[1]);
+          } else {
+            const uint2 v = *reinterpret_cast<const uint2*>(&S.raw[s][raw_off(row) + ch * 8]);
+            const uint32_t raw[2] = {v.x, v.y};
+            *reinterpret_cast<uint4*>(&S.b[s][swz128(row, ch)]) = expand16<BIT>(raw, lut, false);
+          }
         }
 #ifdef DMOQ_TC_PROFILE
         prof_acc[6] += clock64() - prof_r1;
@@ -576,7 +607,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
           *p = expand16<8>(raw, lut, true);
         }
       }
-      const uint32_t slot = j % kScaleRing;
+      const uint32_t slot = (j / SUB) % kScaleRing;   // one slot per group (both steps of an fp16 group store the same values)
       uint16_t sc_h = sc_q[0];
 #pragma unroll
       for (int i = 1; i <= kLag; ++i) {
@@ -610,7 +641,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       return rw;
     };
 
-    uint32_t it = 0, done = 0;
+    uint32_t it = 0, done = 0;    // operand steps issued / published (SUB steps per group)
 #ifdef DMOQ_TC_PROFILE
     const long long prof_start = clock64();
 #endif
@@ -627,7 +658,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       const int seg0 = a.is_down ? nb * kBN : tile.rank * 2 * a.inter + nb * (kBN / 2);
       const int seg1 = a.is_down ? seg0 : seg0 + a.inter;
       const int own_n = a.is_down ? seg0 + sc_i : ((sc_i & 1) ? seg1 : seg0) + (sc_i >> 1);
-      for (int g = 0; g < G; ++g, ++it) {
+      for (int gs = 0; gs < G * SUB; ++gs, ++it) {
+        const int g = gs / SUB, hh = gs % SUB;   // group, and which 128-byte half of its operand rows
         const int s = it % kStages;
         PROF_BEGIN();
         mbar_wait(&S.empty[s], ((it / kStages) & 1) ^ 1, abort_flag);
@@ -636,7 +668,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
 #pragma unroll
         for (int i = 0; i < kCPT; ++i) {
           const int rr = (pt >> 3) + 32 * i, ch = pt & 7;
-          const uint8_t* src = a.a_codes + (size_t)(rw.cp[i] < 0 ? 0 : rw.cp[i]) * a.a_stride + (size_t)g * kG + ch * 16;
+          const uint8_t* src = a.a_codes + ((size_t)(rw.cp[i] < 0 ? 0 : rw.cp[i]) * a.a_stride + (size_t)g * kG) * ES +
+                               hh * 128 + ch * 16;
           cp_async16_zfill(&S.a[s][swz128(rr, ch)], src, rw.cp[i] >= 0);
         }
         PROF_END(4);
@@ -652,7 +685,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
         // scale of this group: loaded now, stored when the group is published
 #pragma unroll
         for (int i = kLag; i > 0; --i) sc_q[i] = sc_q[i - 1];
-        if (stages_xs) sc_q[0] = rw.own >= 0 ? a.a_scales[(size_t)rw.own * xs_per_row + g] : (uint16_t)0;
+        if (stages_xs) sc_q[0] = (MODE != DMOQ_A16 && rw.own >= 0) ? a.a_scales[(size_t)rw.own * xs_per_row + g] : (uint16_t)0;
         else sc_q[0] = a.norm[(size_t)(gg0 + g) * n_total + own_n];
         if (it - done >= (uint32_t)kLag) {
           PROF_BEGIN();
@@ -681,19 +714,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
       // ========================================================================= MMA warp
       constexpr uint32_t idesc_i8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
       constexpr uint32_t idesc_f8 = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-      const uint32_t total_groups = (uint32_t)n_items * (uint32_t)G;
+      constexpr uint32_t idesc_f16 = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      const uint32_t total_steps = (uint32_t)n_items * (uint32_t)G * (uint32_t)SUB;
       PROF_DECL;
 #ifdef DMOQ_TC_PROFILE
       const long long prof_start = clock64();
 #endif
-      for (uint32_t it = 0; it < total_groups; ++it) {
+      for (uint32_t it = 0; it < total_steps; ++it) {
         const int s = it % kStages;
-        const uint32_t b = it % kAccBufs;
+        const uint32_t gi = it / SUB, hh = it % SUB;   // group (= accumulator use) and operand step inside it
+        const uint32_t b = gi % kAccBufs;
         PROF_BEGIN();
         bool ok = mbar_wait(&S.full[s], (it / kStages) & 1, abort_flag);
         PROF_END(0);
         PROF_BEGIN();
-        ok = mbar_wait(&S.acc_empty[b], ((it / kAccBufs) & 1) ^ 1, abort_flag) && ok;
+        if (hh == 0) ok = mbar_wait(&S.acc_empty[b], ((gi / kAccBufs) & 1) ^ 1, abort_flag) && ok;
         PROF_END(1);
         tc_fence_after();
         if (lane == 0 && ok) {
@@ -701,12 +736,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
           const uint64_t db = make_desc(smem_u32(&S.b[s][0]));
           const uint32_t d = tmem_base + b * kBN;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {  // K = 32 bytes per instruction: +2 in 16-byte units
+          for (int k = 0; k < 4; ++k) {  // 32 bytes of K per instruction: +2 in 16-byte units
             if (MODE == DMOQ_A8) tc_mma_i8(d, da + 2 * k, db + 2 * k, idesc_i8, 1);  // buffer holds the bias
-            else tc_mma_f8(d, da + 2 * k, db + 2 * k, idesc_f8, k > 0);
+            else if (MODE == DMOQ_FP8) tc_mma_f8(d, da + 2 * k, db + 2 * k, idesc_f8, k > 0);
+            else tc_mma_f16(d, da + 2 * k, db + 2 * k, idesc_f16, (hh > 0 || k > 0) ? 1u : 0u);
           }
           tc_commit(&S.empty[s]);
-          tc_commit(&S.acc_full[b]);
+          if (hh == SUB - 1) tc_commit(&S.acc_full[b]);
         }
         __syncwarp();
       }
@@ -725,7 +761,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
           const int nb = (blockIdx.x + item * stride_w) % NB;
           const int gg0 = a.is_down ? tile.rank * G : 0;
           const int seg0 = a.is_down ? nb * kBN : tile.rank * 2 * a.inter + nb * (kBN / 2);
-          for (int g = 0; g < G; ++g, ++it) {
+          for (int gs = 0; gs < G * SUB; ++gs, ++it) {   // fp16 operands: both steps of a group get the group's indices
+            const int g = gs / SUB;
             const int s = it % kStages;
             if (!mbar_wait(&S.empty[s], ((it / kStages) & 1) ^ 1, abort_flag)) break;
             const uint8_t* gsrc = a.idx + ((size_t)(gg0 + g) * n_total + seg0) * BPG;
@@ -800,6 +837,8 @@ int launch_bit(const TcArgs& a, int bit, int epi, int work_cap, cudaStream_t s) 
 
 // True when the tensor-core kernel covers this pool/direction; other cases use the warp-level MMA kernel.
 bool dmoq_tc_supported(const dmoq_pool_t& p, int is_down, int hidden) {
+  if (p.mode == DMOQ_A16)   // fp16 operands: codebooks of at most four entries, widened indices
+    return p.bit <= 2 && (is_down ? p.dn_idx_wide : p.gu_idx_wide) != nullptr;
   if (p.mode != DMOQ_A8 && p.mode != DMOQ_FP8) return false;
   if (p.bit == 8 && !(p.mode == DMOQ_A8 && p.identity_lut)) return false;
   if (p.bit <= 2 && (is_down ? p.dn_idx_wide : p.gu_idx_wide) == nullptr) return false;   // needs widened indices
@@ -835,7 +874,12 @@ int dmoq_grouped_gemm_tc(const dmoq_route_t* route, const dmoq_pool_t& p, int po
   long long cap = (long long)route->tile_cap * nb;
   const int work_cap = cap > (1 << 30) ? (1 << 30) : (int)cap;
   if (p.mode == DMOQ_A8) return launch_bit<DMOQ_A8>(a, p.bit, epilogue, work_cap, s);
-  return launch_bit<DMOQ_FP8>(a, p.bit, epilogue, work_cap, s);
+  if (p.mode == DMOQ_FP8) return launch_bit<DMOQ_FP8>(a, p.bit, epilogue, work_cap, s);
+  switch (p.bit) {   // fp16 operands
+    case 1: return launch_epi<DMOQ_A16, 1>(a, epilogue, work_cap, s);
+    case 2: return launch_epi<DMOQ_A16, 2>(a, epilogue, work_cap, s);
+    default: return DMOQ_EINVAL;
+  }
 }
 
 #ifdef DMOQ_TC_PROFILE

@@ -222,7 +222,7 @@ def _merged(mode: int, is_down: bool, a_codes: torch.Tensor, a_scales: Optional[
         p.gu_idx, p.gu_norm, p.gu_lut, p.gu_e0 = indices_gf.data_ptr(), norms.data_ptr(), lut.data_ptr(), e0
     p.identity_lut = int(identity)
     wide = None
-    if bit_width <= 2 and mode in (A8, FP8):   # the tensor-core kernel reads these codes widened to 4-bit fields
+    if bit_width <= 2 and mode in (A16, A8, FP8):   # the tensor-core kernel reads these codes widened to 4-bit fields
         wide = torch.empty(indices_gf.shape[:2] + (64,), dtype=torch.uint8, device=dev)
         check(lib.dmoq_widen_indices(ptr(indices_gf), indices_gf.numel(), bit_width, ptr(wide), _stream()),
               "dmoq_widen_indices")

@@ -179,10 +179,10 @@ class _PoolRuntime:
             raise ValueError("hidden and intermediate sizes must be multiples of 128")
         self.gu_idx = _group_first_device(gu["indices_packed"], bit, hidden, device)
         self.dn_idx = _group_first_device(dn["indices_packed"], bit, n_members * inter, device)
-        # the tensor-core GEMM (INT8 / e4m3 modes) reads 1- and 2-bit codes widened to 4-bit fields; the packed
-        # copy stays for the small-batch kernel, which is bound by the index stream
+        # the tensor-core GEMM (fp16 / INT8 / e4m3 operand modes) reads 1- and 2-bit codes widened to 4-bit fields;
+        # the packed copy stays for the warp-level kernel
         self.gu_idx_wide = self.dn_idx_wide = None
-        if bit <= 2 and mode in (A8, FP8):
+        if bit <= 2 and mode in (A16, A8, FP8):
             self.gu_idx_wide, self.dn_idx_wide = _widen_device(self.gu_idx, bit), _widen_device(self.dn_idx, bit)
         lut_g, s_g, e0_g, f_g, ident_g = _mode_lut(mode, bit, gu["codebook"], device)
         lut_d, s_d, e0_d, f_d, ident_d = _mode_lut(mode, bit, dn["codebook"], device)
@@ -306,9 +306,14 @@ class _Engine:
         self.expert_rank = torch.tensor(expert_rank, **i32)
         self.pool_hoisted = torch.tensor([int(p.hoisted) for p in self.pools] + [0] * (MAX_POOLS - len(self.pools)), **i32)
         self.pool_array = (Pool * len(self.pools))()
-        # every pool runs on the tcgen05 GEMM: INT8 / e4m3 activations, and 8-bit pools only with the identity table
-        self.all_tensor_core = all(p.mode in (A8, FP8) and (p.bit != 8 or (p.identity and p.mode == A8))
-                                   for p in self.pools)
+        # small batches: layers whose pools (of more than a few experts) run on the INT8 / e4m3 tcgen05 GEMM keep
+        # 128-row tiles, that kernel is the faster one at every batch size; fp16-operand layers go to the warp-level
+        # kernel's 32-row tiles (their tcgen05 form needs two operand steps per group and is no faster there)
+        def _tc(p):
+            if p.mode == A8:
+                return p.bit != 8 or bool(p.identity)
+            return p.mode == FP8 and p.bit != 8
+        self.all_tensor_core = all(_tc(p) or p.n_members < 8 for p in self.pools)
         self._ws: Dict[int, _Workspace] = {}
         self.last_launches = 0
 
