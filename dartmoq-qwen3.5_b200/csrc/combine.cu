@@ -117,7 +117,9 @@ static int launch_combine(const dmoq_route_t* route, const uint16_t* dn, int32_t
   if (route->T == 0) return DMOQ_OK;
   const long long total = (long long)route->T * (hidden / 8);
   long long blocks = (total + 255) / 256;
-  const long long cap = 8LL * dmoq_sm_count();
+  // one block per 256 chunks, far more blocks than resident slots on purpose: blocks then sweep the tokens in order
+  // (measured faster than a grid-stride loop over a grid of the resident blocks: 0.33 against 0.36-0.38 ms)
+  const long long cap = 1024LL * dmoq_sm_count();
   if (blocks > cap) blocks = cap;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (weighted)
