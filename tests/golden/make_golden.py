@@ -20,7 +20,9 @@ import sys
 
 os.environ.setdefault("TRITON_INTERPRET", "1")
 os.environ.setdefault("PYTHONDONTWRITEBYTECODE", "1")
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("DARTMOQ_REFERENCE", "")
+if not os.path.isdir(REF):
+    sys.exit("usage: make_golden.py <checkout of the reference>   (or set DARTMOQ_REFERENCE)")
 sys.path.insert(0, REF)
 OUT = os.path.dirname(os.path.abspath(__file__))
 
