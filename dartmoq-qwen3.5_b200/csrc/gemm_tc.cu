@@ -546,6 +546,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
     Lut lut;
 #pragma unroll
     for (int q = 0; q < 4; ++q) lut.w[q] = 0;
+    float lut_step = 0.f;          // fp16 operands, uniform 8-bit codebook: codeword i = (i - 128) * step
+    if (MODE == DMOQ_A16 && BIT == 8) lut_step = __half2float(reinterpret_cast<const __half*>(a.lut)[129]);
     if (MODE == DMOQ_A16) {        // up to four fp16 codewords in two registers
       for (int i = 0; i < (1 << BIT) && i < 4; ++i)
         lut.w[i >> 1] |= (uint32_t)reinterpret_cast<const uint16_t*>(a.lut)[i] << (16 * (i & 1));
@@ -598,6 +600,22 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
 #ifdef DMOQ_TC_PROFILE
         prof_acc[6] += clock64() - prof_r1;
 #endif
+      } else if (MODE == DMOQ_A16) {   // uniform 8-bit codebook: codeword = fp16((index - 128) * step), exact in fp32
+#pragma unroll
+        for (int i = 0; i < kCPT; ++i) {
+          const int row = own_row(i), ch = own_chunk(i);
+          const uint2 v = *reinterpret_cast<const uint2*>(&S.raw[s][row * 64 + ch * 8]);
+          const uint32_t wv[2] = {v.x, v.y};
+          uint32_t o[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int b0 = (int)((wv[q >> 1] >> (16 * (q & 1))) & 255u) - 128;
+            const int b1 = (int)((wv[q >> 1] >> (16 * (q & 1) + 8)) & 255u) - 128;
+            const __half2 h2 = __floats2half2_rn(__fmul_rn((float)b0, lut_step), __fmul_rn((float)b1, lut_step));
+            o[q] = *reinterpret_cast<const uint32_t*>(&h2);
+          }
+          *reinterpret_cast<uint4*>(&S.b[s][swz128(row, ch)]) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < kCPT; ++i) {
@@ -673,7 +691,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
           cp_async16_zfill(&S.a[s][swz128(rr, ch)], src, rw.cp[i] >= 0);
         }
         PROF_END(4);
-        if (BIT == 8) {   // 8-bit indices go straight into the operand tile (expanded in place)
+        if (BIT == 8 && MODE == DMOQ_A16) {   // eight index bytes per fp16 chunk into the raw ring (row pitch 64)
+#pragma unroll
+          for (int i = 0; i < kCPT; ++i) {
+            const int row = own_row(i), ch = own_chunk(i);
+            const int n = a.is_down ? seg0 + row : ((row & 1) ? seg1 : seg0) + (row >> 1);
+            cp_async_n(&S.raw[s][row * 64 + ch * 8], a.idx + ((size_t)(gg0 + g) * n_total + n) * BPG + hh * 64 + ch * 8, 8);
+          }
+        } else if (BIT == 8) {   // 8-bit indices go straight into the operand tile (expanded in place)
 #pragma unroll
           for (int i = 0; i < kCPT; ++i) {
             const int row = own_row(i), ch = own_chunk(i);
@@ -837,8 +862,10 @@ int launch_bit(const TcArgs& a, int bit, int epi, int work_cap, cudaStream_t s) 
 
 // True when the tensor-core kernel covers this pool/direction; other cases use the warp-level MMA kernel.
 bool dmoq_tc_supported(const dmoq_pool_t& p, int is_down, int hidden) {
-  if (p.mode == DMOQ_A16)   // fp16 operands: codebooks of at most four entries, widened indices
+  if (p.mode == DMOQ_A16) {   // fp16 operands: codebooks of at most four entries (widened indices), or the uniform 8-bit one
+    if (p.bit == 8) return p.identity_lut != 0;
     return p.bit <= 2 && (is_down ? p.dn_idx_wide : p.gu_idx_wide) != nullptr;
+  }
   if (p.mode != DMOQ_A8 && p.mode != DMOQ_FP8) return false;
   if (p.bit == 8 && !(p.mode == DMOQ_A8 && p.identity_lut)) return false;
   if (p.bit <= 2 && (is_down ? p.dn_idx_wide : p.gu_idx_wide) == nullptr) return false;   // needs widened indices
@@ -878,6 +905,7 @@ int dmoq_grouped_gemm_tc(const dmoq_route_t* route, const dmoq_pool_t& p, int po
   switch (p.bit) {   // fp16 operands
     case 1: return launch_epi<DMOQ_A16, 1>(a, epilogue, work_cap, s);
     case 2: return launch_epi<DMOQ_A16, 2>(a, epilogue, work_cap, s);
+    case 8: return launch_epi<DMOQ_A16, 8>(a, epilogue, work_cap, s);
     default: return DMOQ_EINVAL;
   }
 }

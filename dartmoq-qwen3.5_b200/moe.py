@@ -149,7 +149,12 @@ def _mode_lut(mode: int, bit: int, codebook: torch.Tensor, device):
     """(lut tensor, act_scale, e0, norm_factor, identity) for one codebook in one activation mode."""
     cb = codebook.detach().cpu()
     if mode == A16:
-        return cb.half().to(device).contiguous(), 1.0, 0, 1.0, 0
+        lut16 = cb.half()
+        ident = 0
+        if bit == 8:   # uniform codebook whose fp16 entries are exactly fp16((i - 128) * step): computable, no table needed
+            step = lut16[129].float()
+            ident = int(torch.equal(((torch.arange(256, dtype=torch.float32) - 128.0) * step).half(), lut16))
+        return lut16.to(device).contiguous(), 1.0, 0, 1.0, ident
     if mode == A8:
         if bit == 8 and fmt.is_uniform_codebook(cb):
             return torch.zeros(256, dtype=torch.int8, device=device), fmt.uniform_codebook_step(cb), 0, 1.0, 1
