@@ -7,6 +7,15 @@ experts ``[r*E/N, (r+1)*E/N)``.  One forward is
     ->  all_to_all (counts, then rows)       ->  grouped expert compute on the owner
     ->  all_to_all back                      ->  fixed-order fp32 sum of each token's top-k rows
 
+That is the ``"rows"`` exchange: one row per (token, slot) pair, results bit-identical to the unsharded
+layer.  The ``"gather"`` exchange moves each token once per rank instead of once per slot:
+
+    all_gather (tokens, routing)  ->  own experts over ALL tokens, other ranks' slots masked (-1)
+    ->  all_to_all of one partial row per token  ->  fp32 sum of the partials in rank order
+
+It rounds each rank's partial sum to the activation dtype before the final sum, so it matches the unsharded
+layer to rounding, not bit for bit.
+
 The exchange plumbing below is plain torch + ``torch.distributed`` and device agnostic (NCCL over
 NVLink on GPUs, gloo on CPUs for tests); the expert compute is a callback, on GPUs the libdmoq engine.
 Rows always land in the receiver's own memory before any kernel touches them.
@@ -100,6 +109,51 @@ def ep_forward(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, ex
     return sum_slots(back, plan.inverse(), plan.T, plan.k, x.dtype)
 
 
+def ep_forward_gathered(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, experts_per_rank: int,
+                        local_partial: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
+                        group=None) -> torch.Tensor:
+    """Token-gather exchange.  ``local_partial(x_all, w_all, local_idx_all) -> (T_all, H)`` runs this rank's
+    experts over every rank's tokens; ``local_idx_all`` holds the local expert id of a slot or -1 where the
+    slot belongs to another rank, and the callback returns each token's weighted sum over its local slots
+    (zeros where it has none).  Batches may differ in size between ranks (padded to the largest)."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    T, H = x.shape
+    k = topk_idx.shape[1]
+    counts = torch.empty(world, dtype=torch.int64, device=x.device)
+    dist.all_gather_into_tensor(counts, torch.tensor([T], dtype=torch.int64, device=x.device), group=group)
+    t_max = max(counts.tolist())              # the one host synchronisation of this exchange
+    if t_max == 0:
+        return x.new_zeros(x.shape)
+
+    def padded(t: torch.Tensor, fill: float) -> torch.Tensor:
+        if T == t_max:
+            return t.contiguous()
+        out = t.new_full((t_max,) + tuple(t.shape[1:]), fill)
+        out[:T] = t
+        return out
+
+    x_all = x.new_empty((world * t_max, H))
+    dist.all_gather_into_tensor(x_all, padded(x, 0.0), group=group)
+    # expert ids travel as fp32 beside the weights (exact below 2**24); padding rows carry id -1
+    meta = torch.cat([topk_w.to(torch.float32), topk_idx.to(torch.float32)], 1)
+    meta_all = meta.new_empty((world * t_max, 2 * k))
+    dist.all_gather_into_tensor(meta_all, padded(meta, -1.0), group=group)
+    w_all = meta_all[:, :k].contiguous()
+    idx_all = meta_all[:, k:].to(torch.int64)
+    lo = rank * experts_per_rank
+    mine = (idx_all >= lo) & (idx_all < lo + experts_per_rank)
+    local_idx = torch.where(mine, idx_all - lo, torch.full_like(idx_all, -1))
+    part = local_partial(x_all, w_all, local_idx).contiguous()
+    back = torch.empty_like(part)             # chunk r: rank r's partial rows for this rank's tokens
+    dist.all_to_all_single(back, part, group=group)
+    if T == 0:
+        return x.new_zeros(x.shape)
+    # row of (token t, rank r) is r * t_max + t; add each token's partials in rank order
+    row_of = (torch.arange(world, device=x.device) * t_max).unsqueeze(0) + torch.arange(T, device=x.device).unsqueeze(1)
+    sum_slots = _sum_slots_cuda if back.is_cuda else _sum_slots_torch
+    return sum_slots(back, row_of.reshape(-1), T, world, x.dtype)
+
+
 class ExpertParallelMoE(torch.nn.Module):
     """EP wrapper around a local ``Wx*BitPartitionedGroupMoE`` that holds only this rank's experts.
 
@@ -109,12 +163,22 @@ class ExpertParallelMoE(torch.nn.Module):
     """
 
     def __init__(self, gate, local_moe, num_experts: int, top_k: int, shared_expert=None,
-                 shared_expert_gate=None, group=None):
+                 shared_expert_gate=None, group=None, exchange: str = "rows"):
         super().__init__()
+        if exchange not in ("rows", "gather"):
+            raise ValueError(f"exchange must be 'rows' or 'gather', got {exchange!r}")
+        want_k = top_k if exchange == "gather" else 1
+        if local_moe.top_k != want_k:
+            raise ValueError(f"exchange={exchange!r} needs a local module with top_k={want_k} "
+                             f"(shard_experts(..., top_k={want_k})), got {local_moe.top_k}")
         self.gate, self.local_moe = gate, local_moe
         self.num_experts, self.top_k = num_experts, top_k
         self.shared_expert, self.shared_expert_gate = shared_expert, shared_expert_gate
-        self.group = group
+        self.group, self.exchange = group, exchange
+
+    def _local_partial(self, x_all, w_all, local_idx):
+        eng = self.local_moe._get_engine(x_all.device)
+        return eng.run(x_all, w_all, local_idx, None)
 
     def _local(self, rows, local_expert, weight):
         if rows.shape[0] == 0:
@@ -132,22 +196,26 @@ class ExpertParallelMoE(torch.nn.Module):
         else:
             w, idx = out.softmax(dim=-1).topk(self.top_k, dim=-1)
         world = dist.get_world_size(self.group)
-        y = ep_forward(x, w, idx, self.num_experts // world, self._local, self.group)
+        if self.exchange == "gather":
+            y = ep_forward_gathered(x, w, idx, self.num_experts // world, self._local_partial, self.group)
+        else:
+            y = ep_forward(x, w, idx, self.num_experts // world, self._local, self.group)
         if self.shared_expert is not None and self.shared_expert_gate is not None:
             y = y + self.shared_expert(x) * torch.sigmoid(self.shared_expert_gate(x))
         return y.reshape(b, s, h)
 
 
 @torch.no_grad()
-def shard_experts(moe, lo: int, hi: int):
-    """New module of the same class holding experts ``[lo, hi)`` of ``moe`` (top_k = 1: on the owner every
-    received row is routed to exactly one local expert).  Packed tensors are sliced, not re-quantised; the
+def shard_experts(moe, lo: int, hi: int, top_k: int = 1):
+    """New module of the same class holding experts ``[lo, hi)`` of ``moe``.  ``top_k`` = 1 for the "rows"
+    exchange (on the owner every received row is routed to exactly one local expert), the layer's own top_k
+    for the "gather" exchange (every token keeps its k slots, the other ranks' masked).  Packed tensors are sliced, not re-quantised; the
     down-side rotation seed is advanced to the first kept column group, so the rotations stay those of the
     full layer (seed + 128 * global group)."""
     from .moe import WxA16Weights
 
     cls = type(moe)
-    out = cls(None, hi - lo, moe.hidden_size, moe.intermediate_size, 1, None, None)
+    out = cls(None, hi - lo, moe.hidden_size, moe.intermediate_size, top_k, None, None)
     out.enable_timing = False
     out.enable_rotation_hoist = moe.enable_rotation_hoist
     out.rotation_hoist_threshold = moe.rotation_hoist_threshold

@@ -41,6 +41,17 @@ def _worker(rank, world, port, out_dir):
     we = w[:0] if rank == 1 else w
     ye = ep.ep_forward(xe, we, ie, per_rank, local_compute)
     np.save(os.path.join(out_dir, f"empty_{rank}.npy"), np.array([ye.shape[0] == xe.shape[0]]))
+    # token-gather exchange: every rank sees all tokens, computes its own experts' share, partials summed in rank order
+    def local_partial(x_all, w_all, local_idx):
+        ge = (local_idx + rank * per_rank + 1).to(x_all.dtype)
+        coef = torch.where(local_idx >= 0, ge * w_all, torch.zeros_like(w_all)).sum(1)
+        return x_all * coef.unsqueeze(1)
+
+    yg = ep.ep_forward_gathered(x, w, idx, per_rank, local_partial)
+    np.save(os.path.join(out_dir, f"gather_{rank}.npy"), np.array([torch.allclose(yg, want, rtol=1e-5, atol=1e-6)]))
+    yge = ep.ep_forward_gathered(xe, we, ie, per_rank, local_partial)
+    ok_e = yge.shape[0] == xe.shape[0] and (rank == 1 or torch.allclose(yge, want, rtol=1e-5, atol=1e-6))
+    np.save(os.path.join(out_dir, f"gather_empty_{rank}.npy"), np.array([ok_e]))
     dist.destroy_process_group()
 
 
@@ -50,6 +61,8 @@ def test_ep_forward_two_cpu_ranks(tmp_path):
     for r in range(2):
         assert np.load(tmp_path / f"ok_{r}.npy")[0]
         assert np.load(tmp_path / f"empty_{r}.npy")[0]
+        assert np.load(tmp_path / f"gather_{r}.npy")[0]
+        assert np.load(tmp_path / f"gather_empty_{r}.npy")[0]
 
 
 def test_dispatch_plan_is_a_stable_permutation():
@@ -78,3 +91,4 @@ def test_shard_experts_slices_the_packed_pools():
                 assert p.bit_weights[bs].down_packed["seed"] == w.down_packed["seed"] + offs[bs][4 * i]
                 assert p._offsets_lists()[bs][-1] == offs[bs][4 * i + 4] - offs[bs][4 * i]
     assert type(parts[0]) is type(moe) and parts[0].top_k == 1 and parts[0].num_experts == 4
+    assert ep.shard_experts(moe, 0, 4, top_k=2).top_k == 2

@@ -1,4 +1,5 @@
-"""Expert parallelism on two GPUs (NCCL): the sharded layer equals the single-GPU layer on the same tokens."""
+"""Expert parallelism on two GPUs (NCCL): the sharded layer equals the single-GPU layer on the same tokens
+(bit for bit with the per-slot exchange, to bf16 rounding with the token-gather exchange)."""
 import os
 import sys
 
@@ -28,6 +29,11 @@ def _worker(rank, world, port, out_dir):
         moe = ep.ExpertParallelMoE(full.gate, local, 8, 3)
         got = moe(x.unsqueeze(0))[0]
         res[mode] = bool(torch.equal(got, want))
+        # token-gather exchange: per-rank partial sums are rounded to bf16 before the final sum
+        local_k = ep.shard_experts(full, rank * 4, rank * 4 + 4, top_k=3).to(dev)
+        got_g = ep.ExpertParallelMoE(full.gate, local_k, 8, 3, exchange="gather")(x.unsqueeze(0))[0]
+        rel = float((got_g.float() - want.float()).norm() / want.float().norm())
+        res[mode] = res[mode] and rel < 4e-3       # bf16 rounding of two partials: about 2**-9 each
     dist.barrier()
     np.save(os.path.join(out_dir, f"ep_{rank}.npy"), np.array([res[m] for m in ("wxa8", "wxfp8", "wxa16")]))
     dist.destroy_process_group()
