@@ -22,7 +22,7 @@ Rows always land in the receiver's own memory before any kernel touches them.
 """
 from __future__ import annotations
 
-from typing import Callable
+from typing import Callable, Optional
 
 import torch
 import torch.distributed as dist
@@ -111,11 +111,13 @@ def ep_forward(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, ex
 
 def ep_forward_gathered(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, experts_per_rank: int,
                         local_partial: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
-                        group=None) -> torch.Tensor:
+                        group=None, extra: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Token-gather exchange.  ``local_partial(x_all, w_all, local_idx_all) -> (T_all, H)`` runs this rank's
     experts over every rank's tokens; ``local_idx_all`` holds the local expert id of a slot or -1 where the
     slot belongs to another rank, and the callback returns each token's weighted sum over its local slots
-    (zeros where it has none).  Batches may differ in size between ranks (padded to the largest)."""
+    (zeros where it has none).  Batches may differ in size between ranks (padded to the largest).
+    ``extra`` (T, H), e.g. the token-local shared expert's output, is added as one more partial in the same
+    fp32 sum."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     T, H = x.shape
     k = topk_idx.shape[1]
@@ -124,6 +126,7 @@ def ep_forward_gathered(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.T
     t_max = max(counts.tolist())              # the one host synchronisation of this exchange
     if t_max == 0:
         return x.new_zeros(x.shape)
+    n_part = world + (1 if extra is not None else 0)
 
     def padded(t: torch.Tensor, fill: float) -> torch.Tensor:
         if T == t_max:
@@ -144,14 +147,16 @@ def ep_forward_gathered(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.T
     mine = (idx_all >= lo) & (idx_all < lo + experts_per_rank)
     local_idx = torch.where(mine, idx_all - lo, torch.full_like(idx_all, -1))
     part = local_partial(x_all, w_all, local_idx).contiguous()
-    back = torch.empty_like(part)             # chunk r: rank r's partial rows for this rank's tokens
-    dist.all_to_all_single(back, part, group=group)
+    back = part.new_empty((n_part * t_max, H))   # chunk r: rank r's partial rows for this rank's tokens
+    dist.all_to_all_single(back[:world * t_max], part, group=group)
     if T == 0:
         return x.new_zeros(x.shape)
-    # row of (token t, rank r) is r * t_max + t; add each token's partials in rank order
-    row_of = (torch.arange(world, device=x.device) * t_max).unsqueeze(0) + torch.arange(T, device=x.device).unsqueeze(1)
+    if extra is not None:
+        back[world * t_max:world * t_max + T] = extra
+    # row of (token t, partial r) is r * t_max + t; add each token's partials in that order
+    row_of = (torch.arange(n_part, device=x.device) * t_max).unsqueeze(0) + torch.arange(T, device=x.device).unsqueeze(1)
     sum_slots = _sum_slots_cuda if back.is_cuda else _sum_slots_torch
-    return sum_slots(back, row_of.reshape(-1), T, world, x.dtype)
+    return sum_slots(back, row_of.reshape(-1), T, n_part, x.dtype)
 
 
 class ExpertParallelMoE(torch.nn.Module):
@@ -175,10 +180,32 @@ class ExpertParallelMoE(torch.nn.Module):
         self.num_experts, self.top_k = num_experts, top_k
         self.shared_expert, self.shared_expert_gate = shared_expert, shared_expert_gate
         self.group, self.exchange = group, exchange
+        self._shared_layer: list = []         # [module or None] once resolved; a list keeps it out of the submodules
 
     def _local_partial(self, x_all, w_all, local_idx):
         eng = self.local_moe._get_engine(x_all.device)
         return eng.run(x_all, w_all, local_idx, None)
+
+    def _shared_partial(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """sigmoid(gate(x)) * shared_expert(x) through the library engine: the shared expert as a layer of its
+        own with no routed experts.  None when there is none, or it is not three packed linears on a GPU (the
+        caller then applies the torch modules)."""
+        if self.shared_expert is None or self.shared_expert_gate is None or not x.is_cuda or x.shape[0] == 0:
+            return None
+        if not self._shared_layer:
+            lm = self.local_moe
+            layer = type(lm)(None, 1, lm.hidden_size, lm.intermediate_size, 1, self.shared_expert,
+                             self.shared_expert_gate)
+            layer.enable_timing = False
+            self._shared_layer.append(layer if layer._shared_packs() is not None else None)
+        layer = self._shared_layer[0]
+        if layer is None:
+            return None
+        T = x.shape[0]
+        no_expert = torch.full((T, 1), -1, dtype=torch.int64, device=x.device)
+        no_weight = torch.zeros((T, 1), dtype=torch.float32, device=x.device)
+        shared_w = torch.sigmoid(self.shared_expert_gate(x)).reshape(-1)
+        return layer._get_engine(x.device).run(x, no_weight, no_expert, shared_w)
 
     def _local(self, rows, local_expert, weight):
         if rows.shape[0] == 0:
@@ -196,11 +223,15 @@ class ExpertParallelMoE(torch.nn.Module):
         else:
             w, idx = out.softmax(dim=-1).topk(self.top_k, dim=-1)
         world = dist.get_world_size(self.group)
+        shared = self._shared_partial(x)
         if self.exchange == "gather":
-            y = ep_forward_gathered(x, w, idx, self.num_experts // world, self._local_partial, self.group)
+            y = ep_forward_gathered(x, w, idx, self.num_experts // world, self._local_partial, self.group,
+                                    extra=shared)
         else:
             y = ep_forward(x, w, idx, self.num_experts // world, self._local, self.group)
-        if self.shared_expert is not None and self.shared_expert_gate is not None:
+            if shared is not None:
+                y = y + shared
+        if shared is None and self.shared_expert is not None and self.shared_expert_gate is not None:
             y = y + self.shared_expert(x) * torch.sigmoid(self.shared_expert_gate(x))
         return y.reshape(b, s, h)
 

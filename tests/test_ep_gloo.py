@@ -48,7 +48,9 @@ def _worker(rank, world, port, out_dir):
         return x_all * coef.unsqueeze(1)
 
     yg = ep.ep_forward_gathered(x, w, idx, per_rank, local_partial)
-    np.save(os.path.join(out_dir, f"gather_{rank}.npy"), np.array([torch.allclose(yg, want, rtol=1e-5, atol=1e-6)]))
+    yx = ep.ep_forward_gathered(x, w, idx, per_rank, local_partial, extra=0.5 * x)   # one more partial per token
+    ok_g = torch.allclose(yg, want, rtol=1e-5, atol=1e-6) and torch.allclose(yx, want + 0.5 * x, rtol=1e-5, atol=1e-6)
+    np.save(os.path.join(out_dir, f"gather_{rank}.npy"), np.array([ok_g]))
     yge = ep.ep_forward_gathered(xe, we, ie, per_rank, local_partial)
     ok_e = yge.shape[0] == xe.shape[0] and (rank == 1 or torch.allclose(yge, want, rtol=1e-5, atol=1e-6))
     np.save(os.path.join(out_dir, f"gather_empty_{rank}.npy"), np.array([ok_e]))

@@ -34,6 +34,18 @@ def _worker(rank, world, port, out_dir):
         got_g = ep.ExpertParallelMoE(full.gate, local_k, 8, 3, exchange="gather")(x.unsqueeze(0))[0]
         rel = float((got_g.float() - want.float()).norm() / want.float().norm())
         res[mode] = res[mode] and rel < 4e-3       # bf16 rounding of two partials: about 2**-9 each
+    # with a shared expert (token-local: computed by the token's own rank as a layer of its own)
+    full = synth.build_layer(hidden=256, n_experts=8, top_k=3, inter=256, shared_inter=256,
+                             bit_mix={2: 0.5, 1: 0.25, 4: 0.25}, mode="wxa8", seed=22, device=dev)
+    x = synth.make_activations(150 + 21 * rank, 256, seed=60 + rank, device=dev)
+    want = full(x.unsqueeze(0))[0].float()
+    for exchange, k_local in (("gather", 3), ("rows", 1)):
+        local = ep.shard_experts(full, rank * 4, rank * 4 + 4, top_k=k_local).to(dev)
+        moe = ep.ExpertParallelMoE(full.gate, local, 8, 3, full.shared_expert, full.shared_expert_gate,
+                                   exchange=exchange)
+        got = moe(x.unsqueeze(0))[0].float()
+        used_engine = moe._shared_layer[0] is not None
+        res["wxa8"] = res["wxa8"] and used_engine and float((got - want).norm() / want.norm()) < 4e-3
     dist.barrier()
     np.save(os.path.join(out_dir, f"ep_{rank}.npy"), np.array([res[m] for m in ("wxa8", "wxfp8", "wxa16")]))
     dist.destroy_process_group()

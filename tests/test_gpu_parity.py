@@ -557,6 +557,35 @@ def test_host_streamer_matches_direct_calls():
         assert torch.equal(y, moe(x.to(DEV).unsqueeze(0))[0].cpu())
 
 
+@pytest.mark.parametrize("mode", ["wxa8", "wxa16"])
+@torch.no_grad()
+def test_expert_parallel_building_blocks_on_one_gpu(mode):
+    """What the token-gather exchange relies on, without a second GPU: slots masked with -1 are dropped (the two
+    halves of the experts add up to the whole layer), and the shared expert as a layer of its own equals the
+    shared pool of the full layer bit for bit."""
+    from dartmoq_b200 import ep
+    moe = _layer(mode, seed=31, n_experts=8).to(DEV)
+    x = synth.make_activations(333, 256, seed=5).to(DEV)
+    out = moe.gate(x)
+    tw, ti = out[1:] if isinstance(out, tuple) else out.softmax(dim=-1).topk(3, dim=-1)
+    tw, ti = tw.float(), ti.long()
+    sw = torch.sigmoid(moe.shared_expert_gate(x)).reshape(-1).float()
+    eng = moe._get_engine(DEV)
+    zero_sw = torch.zeros_like(sw)
+    whole = eng.run(x, tw, ti, zero_sw).float().cpu()
+    halves = [eng.run(x, tw, torch.where((ti >= lo) & (ti < lo + 4), ti, torch.full_like(ti, -1)), zero_sw).float().cpu()
+              for lo in (0, 4)]
+    assert rel_fro(halves[0] + halves[1], whole) < 4e-3            # each half is rounded to bf16 once
+    none = torch.full_like(ti, -1)
+    assert torch.count_nonzero(eng.run(x, tw, none, zero_sw)) == 0
+    shared_in_layer = eng.run(x, tw, none, sw).clone()
+    wrap = ep.ExpertParallelMoE(moe.gate, ep.shard_experts(moe, 0, 8), 8, 3, moe.shared_expert, moe.shared_expert_gate)
+    alone = wrap._shared_partial(x)
+    assert wrap._shared_layer[0] is not None and torch.equal(alone, shared_in_layer)
+    dense = (moe.shared_expert(x) * torch.sigmoid(moe.shared_expert_gate(x))).float().cpu()
+    assert rel_fro(alone.float().cpu(), dense) < 2e-2
+
+
 def test_zz_tensor_core_status_word_is_clean():
     """No bounded wait of the tcgen05 kernels ran out during this session."""
     import ctypes
