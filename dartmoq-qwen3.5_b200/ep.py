@@ -111,13 +111,14 @@ def ep_forward(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, ex
 
 def ep_forward_gathered(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, experts_per_rank: int,
                         local_partial: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
-                        group=None, extra: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        group=None, extra=None) -> torch.Tensor:
     """Token-gather exchange.  ``local_partial(x_all, w_all, local_idx_all) -> (T_all, H)`` runs this rank's
     experts over every rank's tokens; ``local_idx_all`` holds the local expert id of a slot or -1 where the
     slot belongs to another rank, and the callback returns each token's weighted sum over its local slots
     (zeros where it has none).  Batches may differ in size between ranks (padded to the largest).
     ``extra`` (T, H), e.g. the token-local shared expert's output, is added as one more partial in the same
-    fp32 sum."""
+    fp32 sum; a zero-argument callable is resolved only when the partials have come back (a caller that
+    computes it on another stream joins that stream there)."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     T, H = x.shape
     k = topk_idx.shape[1]
@@ -152,7 +153,7 @@ def ep_forward_gathered(x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.T
     if T == 0:
         return x.new_zeros(x.shape)
     if extra is not None:
-        back[world * t_max:world * t_max + T] = extra
+        back[world * t_max:world * t_max + T] = extra() if callable(extra) else extra
     # row of (token t, partial r) is r * t_max + t; add each token's partials in that order
     row_of = (torch.arange(n_part, device=x.device) * t_max).unsqueeze(0) + torch.arange(T, device=x.device).unsqueeze(1)
     sum_slots = _sum_slots_cuda if back.is_cuda else _sum_slots_torch
@@ -181,6 +182,7 @@ class ExpertParallelMoE(torch.nn.Module):
         self.shared_expert, self.shared_expert_gate = shared_expert, shared_expert_gate
         self.group, self.exchange = group, exchange
         self._shared_layer: list = []         # [module or None] once resolved; a list keeps it out of the submodules
+        self._side_stream: list = []
 
     def _local_partial(self, x_all, w_all, local_idx):
         eng = self.local_moe._get_engine(x_all.device)
@@ -223,11 +225,29 @@ class ExpertParallelMoE(torch.nn.Module):
         else:
             w, idx = out.softmax(dim=-1).topk(self.top_k, dim=-1)
         world = dist.get_world_size(self.group)
-        shared = self._shared_partial(x)
-        if self.exchange == "gather":
+        if self.exchange == "gather" and x.is_cuda:
+            # the shared expert needs no exchange: it runs on a second stream beside the collectives and the
+            # routed experts, and is joined where the partial rows are summed
+            main = torch.cuda.current_stream()
+            if not self._side_stream:
+                self._side_stream.append(torch.cuda.Stream(device=x.device))
+            side = self._side_stream[0]
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                shared = self._shared_partial(x)
+
+            def joined():
+                main.wait_stream(side)
+                return shared
+
             y = ep_forward_gathered(x, w, idx, self.num_experts // world, self._local_partial, self.group,
-                                    extra=shared)
+                                    extra=joined if shared is not None else None)
+            main.wait_stream(side)
+        elif self.exchange == "gather":
+            shared = None
+            y = ep_forward_gathered(x, w, idx, self.num_experts // world, self._local_partial, self.group)
         else:
+            shared = self._shared_partial(x)
             y = ep_forward(x, w, idx, self.num_experts // world, self._local, self.group)
             if shared is not None:
                 y = y + shared
