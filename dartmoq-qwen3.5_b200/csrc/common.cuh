@@ -22,6 +22,16 @@ static inline int dmoq_ceil_div(int a, int b) { return (a + b - 1) / b; }
 // Number of SMs of the current device, cached per process (read-only query).
 int dmoq_sm_count();
 
+// One-time kernel set-up (cudaFuncSetAttribute) is per DEVICE: a launcher keeps one flag per device ordinal.
+struct DmoqOncePerDevice {
+  bool done[64] = {};
+  bool* slot() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    return &done[dev];
+  }
+};
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -820,15 +820,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(TcArgs a) {
 
 template <int MODE, int BIT, int EPI>
 int launch(const TcArgs& a, int work_cap, cudaStream_t s) {
-  static bool configured = false;
+  static DmoqOncePerDevice once;
+  bool* configured = once.slot();
+  if (configured == nullptr) return DMOQ_EDEVICE;
   const int bytes = (int)sizeof(Smem) + 1024;
-  if (!configured) {
+  if (!*configured) {
     cudaFuncAttributes fa;
     if (cudaFuncGetAttributes(&fa, gemm_tc_kernel<MODE, BIT, EPI>) != cudaSuccess) return DMOQ_ELAUNCH;
     if (fa.numRegs != kRegsLaunch) return DMOQ_ELAUNCH;   // the role budgets were sized for this pool
     if (cudaFuncSetAttribute(gemm_tc_kernel<MODE, BIT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
       return DMOQ_ELAUNCH;
-    configured = true;
+    *configured = true;
   }
   int grid = dmoq_sm_count();
   if (grid > work_cap) grid = work_cap;

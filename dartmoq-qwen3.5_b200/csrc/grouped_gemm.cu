@@ -488,12 +488,14 @@ constexpr size_t smem_bytes(int bit) {
 
 template <int MODE, int BIT, int EPI, int BM>
 int launch(const GemmArgs& a, int work_cap, cudaStream_t s) {
-  static bool configured = false;
+  static DmoqOncePerDevice once;
+  bool* configured = once.slot();
+  if (configured == nullptr) return DMOQ_EDEVICE;
   const size_t bytes = smem_bytes<MODE, BM>(BIT);
-  if (!configured) {
+  if (!*configured) {
     if (cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BIT, EPI, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
       return DMOQ_ELAUNCH;
-    configured = true;
+    *configured = true;
   }
   int grid = dmoq_sm_count();
   if (grid > work_cap) grid = work_cap;

@@ -226,11 +226,13 @@ constexpr size_t kSmemBytes = (size_t)(kG * kPPitch + kG * kXPitch) * sizeof(flo
 
 template <int MODE>
 int launch_rows(const RotArgs& a, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
+  static DmoqOncePerDevice once;
+  bool* configured = once.slot();
+  if (configured == nullptr) return DMOQ_EDEVICE;
+  if (!*configured) {
     if (cudaFuncSetAttribute(rotq_rows_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess)
       return DMOQ_ELAUNCH;
-    configured = true;
+    *configured = true;
   }
   const int G = a.K / kG;
   const int n_blocks = dmoq_ceil_div(a.n_rows, kRows);
@@ -245,11 +247,13 @@ int launch_rows(const RotArgs& a, cudaStream_t s) {
 
 template <int MODE>
 int launch_tiles(const RotArgs& a, int tile_cap, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
+  static DmoqOncePerDevice once;
+  bool* configured = once.slot();
+  if (configured == nullptr) return DMOQ_EDEVICE;
+  if (!*configured) {
     if (cudaFuncSetAttribute(rotq_tiles_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) != cudaSuccess)
       return DMOQ_ELAUNCH;
-    configured = true;
+    *configured = true;
   }
   const int G = a.K / kG;
   // two blocks are resident per SM: the grid must not exceed those slots, or the blocks left over run alone

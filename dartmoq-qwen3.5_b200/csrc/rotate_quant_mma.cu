@@ -500,11 +500,13 @@ __global__ void __launch_bounds__(kThreads, 2) rotq_mma_tiles_kernel(RotArgs a) 
 
 template <int MODE>
 int launch_rows(const RotArgs& a, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
+  static DmoqOncePerDevice once;
+  bool* configured = once.slot();
+  if (configured == nullptr) return DMOQ_EDEVICE;
+  if (!*configured) {
     if (cudaFuncSetAttribute(rotq_mma_rows_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) != cudaSuccess)
       return DMOQ_ELAUNCH;
-    configured = true;
+    *configured = true;
   }
   const int G = a.K / kG;
   const int n_blocks = dmoq_ceil_div(a.n_rows, kRows);
@@ -519,11 +521,13 @@ int launch_rows(const RotArgs& a, cudaStream_t s) {
 
 template <int MODE>
 int launch_tiles(const RotArgs& a, int tile_cap, cudaStream_t s) {
-  static bool configured = false;
-  if (!configured) {
+  static DmoqOncePerDevice once;
+  bool* configured = once.slot();
+  if (configured == nullptr) return DMOQ_EDEVICE;
+  if (!*configured) {
     if (cudaFuncSetAttribute(rotq_mma_tiles_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem) != cudaSuccess)
       return DMOQ_ELAUNCH;
-    configured = true;
+    *configured = true;
   }
   const int G = a.K / kG;
   // two blocks are resident per SM: the grid must not exceed those slots, or the blocks left over run alone

@@ -315,12 +315,14 @@ int launch_route(const RouteArgs& a, bool fused, cudaStream_t s) {
   const size_t e_bytes = (size_t)r.E * sizeof(int32_t);
   const size_t place_bytes = place_smem_bytes(r.E) + 16;
   const size_t fused_bytes = place_bytes + e_bytes + 16;
-  static bool configured = false;
-  if (!configured) {  // up to 4096 experts: the placement tables can exceed the default 48 KiB
+  static DmoqOncePerDevice once;
+  bool* configured = once.slot();
+  if (configured == nullptr) return DMOQ_EDEVICE;
+  if (!*configured) {  // up to 4096 experts: the placement tables can exceed the default 48 KiB
     if (cudaFuncSetAttribute(route_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(route_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess)
       return DMOQ_ELAUNCH;
-    configured = true;
+    *configured = true;
   }
   if (fused) {
     route_fused_kernel<<<1, 1024, fused_bytes, s>>>(a);

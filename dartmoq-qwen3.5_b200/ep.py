@@ -177,6 +177,10 @@ class ExpertParallelMoE(torch.nn.Module):
         if local_moe.top_k != want_k:
             raise ValueError(f"exchange={exchange!r} needs a local module with top_k={want_k} "
                              f"(shard_experts(..., top_k={want_k})), got {local_moe.top_k}")
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        if num_experts % world:
+            raise ValueError(f"num_experts ({num_experts}) must be a multiple of the group size ({world}): "
+                             "every rank owns the same number of experts")
         self.gate, self.local_moe = gate, local_moe
         self.num_experts, self.top_k = num_experts, top_k
         self.shared_expert, self.shared_expert_gate = shared_expert, shared_expert_gate

@@ -40,6 +40,26 @@ def _need_cuda(t: torch.Tensor) -> None:
         raise _lib.DmoqError("libdmoq operators take CUDA tensors only (no CPU path)")
 
 
+def _on_tensor_device(fn):
+    """Run ``fn`` with the device of its first tensor argument current, so that the stream handed to the
+    library and every allocation belong to that device whichever one the caller has selected; all tensor
+    arguments must live there."""
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        tensors = [a for a in list(args) + list(kwargs.values()) if isinstance(a, torch.Tensor)]
+        if not tensors or not tensors[0].is_cuda:
+            return fn(*args, **kwargs)
+        dev = tensors[0].device
+        for t in tensors:
+            if t.is_cuda and t.device != dev:
+                raise ValueError(f"all tensors must be on {dev}, got one on {t.device}")
+        with torch.cuda.device(dev):
+            return fn(*args, **kwargs)
+    return wrapper
+
+
 def _check_rot(x, rot, group_size, num_groups):
     if group_size != GROUP:
         raise ValueError(f"group_size must be {GROUP}, got {group_size}")
@@ -51,6 +71,7 @@ def _check_rot(x, rot, group_size, num_groups):
         raise TypeError(f"x must be fp16 or bf16, got {x.dtype}")
 
 
+@_on_tensor_device
 def _rotate(mode: int, x: torch.Tensor, rot: torch.Tensor, extra_scale: float, codes, scales,
             src_row: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> None:
     _need_cuda(x)
@@ -117,6 +138,7 @@ def batch_rotate_input(x: torch.Tensor, group_size: int, seed_base: int) -> torc
     return out
 
 
+@_on_tensor_device
 def convert_to_group_first(indices_packed: torch.Tensor, norms: torch.Tensor, group_size: int, bit_width: int):
     """(N, K*b/8) -> (G, N, gs*b/8) on the device; norms (N, G) -> (G, N)."""
     if bit_width not in fmt.SUPPORTED_BITS:
@@ -163,6 +185,7 @@ class _HostRoute:
         self.c = r
 
 
+@_on_tensor_device
 def router_topk(logits: torch.Tensor, top_k: int, renormalize: bool = False):
     """fp32 softmax over experts -> top-k probabilities (descending) and indices (int64), optionally renormalised:
     the router stage of the module (quantization/wxa16/bit_partitioned_moe.py:1113-1119) as one launch."""
@@ -176,6 +199,7 @@ def router_topk(logits: torch.Tensor, top_k: int, renormalize: bool = False):
     return w, idx
 
 
+@_on_tensor_device
 def _merged(mode: int, is_down: bool, a_codes: torch.Tensor, a_scales: Optional[torch.Tensor], a_stride: int,
             indices_gf: torch.Tensor, lut: torch.Tensor, norms_gf: torch.Tensor, expert_info, group_size: int,
             bit_width: int, norms_prescaled: bool, *, e0: int = 0, identity: bool = False,

@@ -236,6 +236,8 @@ class _Workspace:
 class _Engine:
     """Everything a module needs on one device in one activation mode."""
 
+    WORKSPACE_CACHE = 16   # per-token-count buffer sets kept (a serving loop sees many batch sizes)
+
     def __init__(self, module: "WxA16BitPartitionedGroupMoE", device):
         self.device = device
         self.lib = _lib.load()
@@ -324,10 +326,13 @@ class _Engine:
 
     # ------------------------------------------------------------------ per-T buffers
     def workspace(self, T: int) -> _Workspace:
-        ws = self._ws.get(T)
+        ws = self._ws.pop(T, None)
         if ws is not None:
+            self._ws[T] = ws          # most recently used last
             return ws
-        if len(self._ws) >= 4:
+        # least recently used first; a captured graph keeps its own reference to the workspace it was
+        # captured with, so dropping an entry here never frees memory a graph still replays against
+        if len(self._ws) >= self.WORKSPACE_CACHE:
             self._ws.pop(next(iter(self._ws)))
         dev = self.device
         ws = _Workspace()
@@ -588,6 +593,7 @@ class WxA16BitPartitionedGroupMoE(nn.Module):
             raise TypeError(f"expected WxA16BitPartitionedGroupMoE, got {type(moe)}")
         moe.__class__ = cls
         moe._engine = None
+        moe._graphs = None     # captured graphs belong to the old engine's buffers and activation mode
         return moe
 
     # ------------------------------------------------------------------ helpers
@@ -628,6 +634,7 @@ class WxA16BitPartitionedGroupMoE(nn.Module):
         if eng is None or eng.device != device:
             eng = _Engine(self, device)
             self._engine = eng
+            self._graphs = None
         return eng
 
     def _body(self, eng, x, prof=None, partials=None):
@@ -667,9 +674,11 @@ class WxA16BitPartitionedGroupMoE(nn.Module):
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 static_y = self._body(eng, static_x)
-            entry = (graph, static_x, static_y)
+            # the graph replays raw pointers into the engine's tensors and into this token count's workspace:
+            # the entry keeps both alive for as long as the graph exists
+            entry = (graph, static_x, static_y, eng, eng.workspace(x.shape[0]))
             self._graphs[key] = entry
-        graph, static_x, static_y = entry
+        graph, static_x, static_y = entry[:3]
         static_x.copy_(x)
         graph.replay()
         return static_y.clone()
@@ -685,7 +694,19 @@ class WxA16BitPartitionedGroupMoE(nn.Module):
         device = next(self.gate.parameters()).device
         dummy = torch.randn(batch_size, seq_len, self.hidden_size, device=device, dtype=self.gate.weight.dtype)
         self.forward(dummy)
-        torch.cuda.synchronize()
+        torch.cuda.synchronize(device)
+        with torch.cuda.device(device):
+            self.check_device_status()
+
+    @staticmethod
+    def check_device_status() -> None:
+        """Raise if a bounded wait of the tensor-core kernels ever ran out on the current device (the launch that
+        hit it wrote unspecified output).  Synchronises the device; ``forward`` itself never does, so callers that
+        want this check poll it at their own synchronisation points."""
+        st = C.c_int32(0)
+        check(_lib.load().dmoq_tc_status(C.byref(st)), "dmoq_tc_status")
+        if st.value != 0:
+            raise _lib.DmoqError(f"tensor-core kernel status word is {st.value}: a bounded device-side wait timed out")
 
     # ------------------------------------------------------------------ forward
     @torch.no_grad()
@@ -699,19 +720,23 @@ class WxA16BitPartitionedGroupMoE(nn.Module):
         x = hidden_states.reshape(-1, h).contiguous()
         if x.shape[0] == 0:
             return torch.zeros_like(hidden_states)
-        eng = self._get_engine(x.device)
-        prof = _EventProfiler() if self.enable_cuda_profile else None
+        # every launch goes to the current stream of the tensors' own device, whichever device is current
+        # for the caller (a model sharded over several GPUs in one process calls layers on all of them)
+        with torch.cuda.device(x.device):
+            eng = self._get_engine(x.device)
+            prof = _EventProfiler() if self.enable_cuda_profile else None
 
-        graphed = (self.enable_cuda_graph and prof is None and _partials is None
-                   and x.shape[0] <= self.cuda_graph_max_tokens and not torch.cuda.is_current_stream_capturing())
-        if graphed:
-            y = self._run_graphed(eng, x)
-        else:
-            y = self._body(eng, x, prof, _partials)
-        if eng.shared_torch:
-            y = y + self.shared_expert(x) * torch.sigmoid(self.shared_expert_gate(x))
-        if prof is not None:
-            self.last_cuda_stats = prof.stats()
+            graphed = (self.enable_cuda_graph and prof is None and _partials is None
+                       and x.shape[0] <= self.cuda_graph_max_tokens and not torch.cuda.is_current_stream_capturing())
+            if graphed:
+                y = self._run_graphed(eng, x)
+            else:
+                y = self._body(eng, x, prof, _partials)
+            if eng.shared_torch:
+                y = y + self.shared_expert(x) * torch.sigmoid(self.shared_expert_gate(x))
+            if prof is not None:
+                self.last_cuda_stats = prof.stats()
+                self.check_device_status()    # the profiler has synchronised already
         if self.enable_timing:
             self.last_timings = {"total": time.time() - t0, "active_bits": len(eng.pools)}
         return y.reshape(b, s, h)

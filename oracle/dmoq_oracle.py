@@ -334,8 +334,12 @@ def gemm_int8(x_i8: np.ndarray, xs_f16: np.ndarray, w_i8: np.ndarray, norm_f16: 
     """
     b = x_i8.shape[0]
     g, n, _ = w_i8.shape
-    xg = x_i8.reshape(b, g, GS).astype(np.int32)
-    part = np.einsum("bgk,gnk->bng", xg, w_i8.astype(np.int32), optimize=True).astype(np.int32)
+    # integer group sums through fp32 matrix products: every product and every partial sum is an integer of
+    # magnitude <= 128*127*127 < 2^24, so fp32 arithmetic is exact whatever the summation order
+    xg = x_i8.reshape(b, g, GS).astype(np.float32)
+    part = np.empty((b, n, g), np.int32)
+    for gi in range(g):
+        part[:, :, gi] = (xg[:, gi] @ w_i8[gi].astype(np.float32).T).astype(np.int32)
     total = np.zeros((b, n), np.float32)
     xs = xs_f16.astype(np.float32)
     nm = norm_f16.astype(np.float32)
@@ -511,17 +515,17 @@ def moe_forward(layer: Layer, x: torch.Tensor, topk_w: np.ndarray, topk_idx: np.
         vals, rs, block, codes, scales = _quant_act(mode, acc, ex_g, e0_g)
         n_rows = rows_tok.size
         gu_out = np.zeros((n_rows, 2 * inter), np.float16)
-        parts_g = np.zeros((n_rows, 2 * inter, G_h), np.int32) if mode == "wxa8" else None
+        parts_g = np.zeros((n_rows, 2 * inter, G_h), np.int32) if (mode == "wxa8" and keep) else None
         for rank, r0, n in seg:
             w_idx = weight_codes(gu["idx_gf"], bit, slice(2 * inter * rank, 2 * inter * (rank + 1)), slice(0, G_h))
             o, pt = _pool_gemm(mode, vals[r0:r0 + n], None if rs is None else rs[r0:r0 + n], block, w_idx, tab_g,
                                norm_g[:, 2 * inter * rank:2 * inter * (rank + 1)])
             gu_out[r0:r0 + n] = o
-            if pt is not None:
+            if parts_g is not None:
                 parts_g[r0:r0 + n] = pt
         act = silu_mul_f16(gu_out, inter)
         dn_out = np.zeros((n_rows, H), np.float16)
-        parts_d = np.zeros((n_rows, H, G_i), np.int32) if mode == "wxa8" else None
+        parts_d = np.zeros((n_rows, H, G_i), np.int32) if (mode == "wxa8" and keep) else None
         d_codes, d_scales = [], []
         for rank, r0, n in seg:
             rot = rotation_stack_f16(dn["seed"] + rank * inter, G_i)
@@ -532,7 +536,7 @@ def moe_forward(layer: Layer, x: torch.Tensor, topk_w: np.ndarray, topk_idx: np.
             w_idx = weight_codes(dn["idx_gf"], bit, slice(0, H), slice(rank * G_i, (rank + 1) * G_i))
             o, pt = _pool_gemm(mode, v2, rs2, blk2, w_idx, tab_d, norm_d[rank * G_i:(rank + 1) * G_i])
             dn_out[r0:r0 + n] = o
-            if pt is not None:
+            if parts_d is not None:
                 parts_d[r0:r0 + n] = pt
         # dn.to(bf16); dn.mul_(w); final.index_add_(0, tokens, dn)   (wxa16/...:960-967)
         contrib = torch.from_numpy(dn_out).to(torch.bfloat16)

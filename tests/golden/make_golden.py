@@ -287,7 +287,81 @@ def gen_module():
     save("module", **out)
 
 
+def gen_checkpoint():
+    """The reference's own from_build_block (pool layout + quantisation) and save_quantized_model on a tiny model:
+    staged fp16 sub-expert weights -> packed pools, and the meta.json / model.safetensors pair it writes."""
+    import shutil
+    import torch.nn as nn
+    import qwen35_quant_io as r_io
+    from quantization.wxa16.bit_partitioned_moe import WxA16BitPartitionedGroupMoE
+    from quantization.wxa16.linear import WxA16Linear
+
+    H, E = 128, 4
+    g = torch.Generator().manual_seed(23)
+    # neurons of every expert per bit width: expert 1 is split over two widths, expert 3 has no 4-bit part
+    neurons = {0: {4: 128}, 1: {4: 128, 2: 128}, 2: {2: 256}, 3: {2: 128}}
+
+    class Sub(nn.Module):
+        def __init__(self, bit, n):
+            super().__init__()
+            self._quant_bit = bit
+            self.gate_proj, self.up_proj = nn.Linear(H, n, bias=False), nn.Linear(H, n, bias=False)
+            self.down_proj = nn.Linear(n, H, bias=False)
+            for lin in (self.gate_proj, self.up_proj, self.down_proj):
+                lin.weight.data.copy_(torch.randn(lin.weight.shape, generator=g) * 0.02)
+
+    class Wrapper(nn.Module):
+        def __init__(self, parts):
+            super().__init__()
+            self.sub_experts = nn.ModuleList([Sub(b, n) for b, n in parts.items()])
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate = nn.Linear(H, E, bias=False)
+            self.top_k = 2
+            self.experts = nn.ModuleList([Wrapper(neurons[e]) for e in range(E)])
+            mk = lambda i, o: WxA16Linear.from_linear(nn.Linear(i, o, bias=False), 8, 128, seed=77, uniform_codebook=True)
+            self.shared_expert = nn.Module()
+            self.shared_expert.gate_proj, self.shared_expert.up_proj = mk(H, 128), mk(H, 128)
+            self.shared_expert.down_proj = mk(128, H)
+            self.shared_expert_gate = nn.Linear(H, 1, bias=False)
+
+    torch.manual_seed(5)
+    block = Block()
+    out = {}
+    for e in range(E):
+        for sub in block.experts[e].sub_experts:
+            for name in ("gate_proj", "up_proj", "down_proj"):
+                out[f"w_{e}_{sub._quant_bit}_{name}"] = getattr(sub, name).weight.data.clone().numpy()
+    md = {"num_experts": E, "hidden_size": H, "intermediate_size": 256, "bit_list": [4, 2],
+          "expert_bit_indices": [{b: list(range(n)) for b, n in neurons[e].items()} for e in range(E)]}
+    moe = WxA16BitPartitionedGroupMoE.from_build_block(block, md, group_size=128)
+    for bs, w in moe.bit_weights.items():
+        for side, pk in (("gate_up", w.gate_up_packed), ("down", w.down_packed)):
+            for k in ("indices_packed", "norms", "codebook"):
+                out[f"{side}_{k}_{bs}"] = u8(pk[k]) if pk[k].dtype == torch.uint8 else pk[k].clone().numpy()
+            out[f"{side}_seed_{bs}"] = np.array(int(pk["seed"]))
+        out[f"offsets_{bs}"] = moe.expert_offsets[bs].numpy()
+    save("build_block", **out)
+
+    class Layer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.mlp = moe
+            self.self_attn = nn.Module()
+            self.self_attn.q_proj = WxA16Linear.from_linear(nn.Linear(H, 256, bias=True), 8, 128, seed=78,
+                                                             uniform_codebook=True)
+
+    model = nn.Module()
+    model.model = nn.Module()
+    model.model.layers = nn.ModuleList([Layer()])
+    ckpt = os.path.join(OUT, "ckpt_ref")
+    shutil.rmtree(ckpt, ignore_errors=True)
+    r_io.save_quantized_model(model, ckpt, base_model_path=None, quant_args={"seed": 0}, verbose=False)
+
+
 if __name__ == "__main__":
-    which = sys.argv[2:] or ["format", "quantizer", "actquant", "merged_gemm", "module"]
+    which = sys.argv[2:] or ["format", "quantizer", "actquant", "merged_gemm", "module", "checkpoint"]
     for name in which:
         globals()["gen_" + name]()
