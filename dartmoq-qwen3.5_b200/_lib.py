@@ -31,6 +31,7 @@ class Pool(C.Structure):
         ("gu_rot", C.c_void_p), ("dn_rot", C.c_void_p),
         ("act_codes", C.c_void_p), ("act_scales", C.c_void_p),
         ("gu_idx_wide", C.c_void_p), ("dn_idx_wide", C.c_void_p),
+        ("gu_img", C.c_void_p), ("dn_img", C.c_void_p), ("gu_norm_img", C.c_void_p), ("dn_norm_img", C.c_void_p),
     ]
 
 
@@ -70,6 +71,8 @@ EXPORTS = {
     "dmoq_combine_weighted": (C.c_int, [C.POINTER(Route), C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "dmoq_convert_group_first": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "dmoq_widen_indices": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
+    "dmoq_weight_image_bytes": (C.c_size_t, [C.POINTER(Pool), C.c_int32, C.c_int32]),
+    "dmoq_expand_weights": (C.c_int, [C.POINTER(Pool), C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
 }
 
 _lib = None

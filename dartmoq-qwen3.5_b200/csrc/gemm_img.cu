@@ -1,0 +1,731 @@
+// Grouped GEMM over "weight images" on the 5th-generation tensor cores (tcgen05 + TMEM), all four activation modes.
+//
+// A weight image is a pool's weights already looked up in the mode's codeword table and laid out as tensor-core
+// operand rows (dmoq_expand_weights): (groups, image rows, 128 columns) of int8 / e4m3 / fp16 codewords, or packed
+// e2m1 nibbles with two groups per 128-byte row.  Its tiles need no work in this kernel: one thread brings each
+// 128 x 128-byte tile into shared memory with a TMA tensor-map copy (cp.async.bulk.tensor, 128-byte swizzle), so an
+// expert that receives many rows pays for the table lookup once per forward (or once at load time) instead of once
+// per 128-row tile.  The math is that of the reference's merged kernels:
+//   turboquant_utils/triton_kernels.py:1375 (A16), triton_kernels_a8.py:825 (A8, int32 sums per 128-group),
+//   triton_kernels_fp8.py:532 (FP8), triton_kernels_fp4.py:587 (FP4: e2m1 x e2m1 with per-32 e8m0 block scales,
+//   weights folded to e2m1 at load time, W_FOLDED).
+//
+// One persistent CTA of 768 threads per SM:
+//   warps 0-15   epilogue: warp w drains lanes 32*(w%4).. of columns 32*(w/4).. of the group's accumulator
+//                (tcgen05.ld 32x32b: a thread owns one row), folds (acc * row_scale) * col_norm into an fp32 running
+//                total, and at the end of a tile writes SiLU*up / plain / weighted rows straight to global memory
+//   warps 16-19  producers: thread = tile row; gather the row's activation codes with cp.async into the swizzled A
+//                tile; thread 0 also issues the TMA copy of the B tile and the bulk copy of the group's column norms;
+//                in FP4 mode they store the rows' e8m0 block scales into TMEM (tcgen05.st) for the block-scaled MMA
+//   warp 20      one thread issues tcgen05.mma: kind::i8 / f8f6f4 / f16, or kind::mxf4nvf4.block_scale (scale_vec 2X)
+//   warps 21-23  idle (setmaxnreg moves their registers to the epilogue)
+// Every mbarrier wait is bounded; on a timeout the CTA raises the device status word, stops issuing work and
+// falls through to the common teardown, where TMEM is released.
+#include <cuda.h>
+
+#include "common.cuh"
+
+// raised when a bounded wait of this file's kernels runs out (read through dmoq_tc_status)
+__device__ int g_dmoq_img_status = 0;
+
+namespace {
+
+constexpr int kBM = 128, kBN = 128, kG = DMOQ_GROUP;
+constexpr int kStages = 4;          // operand ring depth: one 128-row x 128-byte tile of A and of B per stage
+constexpr int kLag = 2;             // producers publish a stage this many stages after issuing its copies
+constexpr int kEpiWarps = 16, kProdWarps = 4;
+constexpr int kThreads = 32 * (kEpiWarps + kProdWarps + 4);
+constexpr int kMmaWarp = kEpiWarps + kProdWarps;
+constexpr int kNormRing = 16;       // column-norm slots; must exceed the groups in flight (2*kStages + accumulators)
+// setmaxnreg moves registers between warpgroups inside the pool the block got at launch (768 threads x 80); asking
+// for more than the pool holds blocks forever, so the launcher checks the compiled register count.
+constexpr int kRegsLaunch = 80;
+constexpr int kRegsEpi = 96, kRegsProd = 48, kRegsMma = 40;
+static_assert(32 * (kEpiWarps * kRegsEpi + kProdWarps * kRegsProd + 4 * kRegsMma) <= kRegsLaunch * kThreads,
+              "role register budgets exceed the block's register pool");
+constexpr int kTileB = kBM * 128;   // bytes of one operand tile
+constexpr uint32_t kSpinLimit = 1u << 26;
+constexpr long long kWaitCycles = 2000000000LL;
+// INT8 accumulators start from the bit pattern of 1.5*2^23: the int32 sum read back as fp32 is 12582912 + sum
+// exactly (|sum| <= 128*127*127 < 2^22), which saves the integer->float conversion.
+constexpr uint32_t kMagicBits = 0x4B400000u;
+constexpr float kMagicFloat = 12582912.0f;
+constexpr int kTmemCols = 512;
+constexpr int kSfaCol = 384;        // FP4: three accumulators, then the scale-factor columns
+constexpr int kSfbCol = kSfaCol + kStages * 2 * 4;
+
+struct ImgArgs {
+  const DmoqTile* tiles;
+  const int32_t* n_tiles;
+  const int32_t* a_row;       // gather map (gate_up) or null (down: the row's own index)
+  const float* row_weight;
+  int pool, is_down, inter, hidden;
+  const float* norm_img;      // (groups, n_img) fp32, image row order
+  int n_img;                  // image rows per group
+  const uint8_t* a_codes;
+  const uint8_t* a_scales;    // A8/FP8: fp16 (rows, K/128); FP4: e8m0 bytes (rows, K/32)
+  int a_stride;               // row pitch of the code table in elements
+  void* out;
+  int out_stride;
+  int32_t* partials;
+  uint32_t sfb_word;          // FP4: the weight block scale byte 127+E0 replicated four times
+};
+
+// ------------------------------------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait (about one second).  Returns false, and raises the abort flag, if the phase never completes; once
+// the flag is up every later wait returns at once.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_flag) return false;
+  const long long t0 = clock64();
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_try_wait_suspend(bar, parity, 100000u)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) break;
+  }
+  *abort_flag = 1;
+  atomicOr(&g_dmoq_img_status, 1);
+  return false;
+}
+// Time-bounded wait that ignores the abort flag: used at teardown so that no bulk copy is still writing into this
+// block's shared memory when it exits.
+__device__ __forceinline__ void mbar_wait_quiet(uint64_t* bar, uint32_t parity) {
+  const long long t0 = clock64();
+  while (!mbar_try_wait_suspend(bar, parity, 100000u)) {
+    if (clock64() - t0 > kWaitCycles) break;
+  }
+}
+// 2-D tile of a tensor map -> this block's shared memory; completion counted in bytes on the barrier.  The map lies
+// over this GPU's own memory; the inner coordinate x is a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+template <int MODE>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  if (MODE == DMOQ_A8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else if (MODE == DMOQ_FP8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// e2m1 x e2m1, one ue8m0 scale per 32 elements of K for each operand, read from TMEM (K = 64 per instruction)
+__device__ __forceinline__ void tc_mma_mxf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// 32 lanes x 32 columns: thread t of the warp receives lane base + t, register j = column base + j
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// 32 lanes x 8 columns of one value
+__device__ __forceinline__ void tc_st8_fill(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(taddr), "r"(v) : "memory");
+}
+// 32 lanes x 4 columns: thread t writes its four values to lane base + t
+__device__ __forceinline__ void tc_st4(uint32_t taddr, uint32_t v0, uint32_t v1, uint32_t v2, uint32_t v3) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(v0), "r"(v1), "r"(v2), "r"(v3)
+               : "memory");
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+
+// K-major, 128-byte swizzle: tile row r is 128 bytes; 16-byte chunk c lives at slot c ^ (r & 7); groups of 8 rows
+// are 1024 bytes apart (the descriptor's stride byte offset).  The TMA copy writes the same pattern.
+__device__ __forceinline__ uint32_t swz128(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+struct Smem {
+  uint8_t a[kStages][kTileB];   // 1024-byte aligned operand tiles
+  uint8_t b[kStages][kTileB];
+  float norm[kNormRing][kBN];   // column norms of a group, image column order
+  uint64_t full[kStages], empty[kStages], acc_full[4], acc_empty[4];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+// Per mode: bytes of an activation element in the A tile, operand steps per group / groups per operand step.
+//   A8, FP8: one 128-byte step per group.  A16: two steps per group (64 fp16 columns each).
+//   FP4: one step carries two groups (64 bytes of packed e2m1 each).
+template <int MODE>
+struct Shape {
+  static constexpr int SPG = (MODE == DMOQ_A16) ? 2 : 1;   // operand steps per group
+  static constexpr int GPS = (MODE == DMOQ_FP4) ? 2 : 1;   // groups per operand step
+  static constexpr int ACC = (MODE == DMOQ_FP4) ? 3 : 4;   // accumulator buffers
+};
+
+template <int MODE, int EPI>
+__global__ void __launch_bounds__(kThreads, 1) gemm_img_kernel(const __grid_constant__ CUtensorMap tmap_b, ImgArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  volatile int* abort_flag = &S.abort_flag;
+  constexpr int SPG = Shape<MODE>::SPG, GPS = Shape<MODE>::GPS, ACC = Shape<MODE>::ACC;
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&S.full[s], kProdWarps + 1);   // four producer warps + the thread that announces the bulk bytes
+      mbar_init(&S.empty[s], 1);
+    }
+    for (int b = 0; b < 4; ++b) {
+      mbar_init(&S.acc_full[b], 1);
+      mbar_init(&S.acc_empty[b], kEpiWarps);
+    }
+    S.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kMmaWarp) {  // the MMA warp owns the TMEM allocation
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&S.tmem_base)), "r"(kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = S.tmem_base;
+  if (MODE == DMOQ_A8 || MODE == DMOQ_FP4) {
+    if (warp < kEpiWarps) {
+      const uint32_t t0 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+      if (MODE == DMOQ_A8) {   // bias every accumulator buffer: this warp's 32 lanes x 32 columns of each
+#pragma unroll
+        for (int b = 0; b < ACC; ++b)
+#pragma unroll
+          for (int q = 0; q < 4; ++q) tc_st8_fill(t0 + b * kBN + (warp >> 2) * 32 + 8 * q, kMagicBits);
+      } else if (warp < 4) {   // the constant weight block scale, for every column and every 32-block of K
+        tc_st4(t0 + kSfbCol, a.sfb_word, a.sfb_word, a.sfb_word, a.sfb_word);
+      }
+      tc_wait_st();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+  }
+
+  const int n_tiles = a.n_tiles[a.pool];
+  const DmoqTile* tiles = a.tiles + a.n_tiles[DMOQ_MAX_POOLS + a.pool];
+  const int NB = a.is_down ? a.hidden / kBN : a.inter / (kBN / 2);
+  const int G = a.is_down ? a.inter / kG : a.hidden / kG;
+  const int steps_per_item = (G * SPG + GPS - 1) / GPS;
+  const int n_work = n_tiles * NB;
+  const int stride_w = gridDim.x;
+  const int n_items = (int)blockIdx.x < n_work ? (n_work - 1 - (int)blockIdx.x) / stride_w + 1 : 0;
+  const DmoqTile kNoTile{0, 0, 0, 0};
+  auto tile_of = [&](int item) {   // item index of this CTA -> tile record (clamped past the end)
+    const int w = blockIdx.x + item * stride_w;
+    return (item < n_items) ? tiles[w / NB] : kNoTile;
+  };
+
+  if (warp < kEpiWarps) {
+    // =========================================================================== epilogue warps
+    reg_inc<kRegsEpi>();
+    const int lq = warp & 3, cq = warp >> 2;
+    const int row = lq * 32 + lane;                  // tile row of this thread
+    const uint32_t t_lane = tmem_base + ((uint32_t)(lq * 32) << 16) + cq * 32;
+    const int xs_per_row = a.a_stride / kG;
+    uint32_t ia = 0;                                 // groups consumed so far
+    DmoqTile next = tile_of(0);
+    for (int item = 0; item < n_items; ++item) {
+      const DmoqTile tile = next;
+      next = tile_of(item + 1);
+      const int nb = (blockIdx.x + item * stride_w) % NB;
+      const bool live = row < tile.rows;
+      const __half* xs_row = nullptr;
+      if (MODE == DMOQ_A8 || MODE == DMOQ_FP8) {
+        const int src = live ? (a.a_row ? a.a_row[tile.row0 + row] : tile.row0 + row) : 0;
+        xs_row = reinterpret_cast<const __half*>(a.a_scales) + (size_t)src * xs_per_row;
+      }
+      float2 total2[16];
+#pragma unroll
+      for (int c = 0; c < 16; ++c) total2[c] = make_float2(0.f, 0.f);
+      float xs_next = (xs_row != nullptr && live) ? __half2float(xs_row[0]) : 0.f;
+
+      for (int g = 0; g < G; ++g, ++ia) {
+        const uint32_t b = ia % ACC, ph = (ia / ACC) & 1;
+        const uint32_t slot = ia % kNormRing;
+        const float xs = xs_next;
+        if (xs_row != nullptr && live && g + 1 < G) xs_next = __half2float(xs_row[g + 1]);   // in flight during this group
+        // The group's norms were bulk-copied before its operand stage completed; the MMA thread saw that completion
+        // before it committed acc_full[], so they are visible here.
+        mbar_wait(&S.acc_full[b], ph, abort_flag);   // on a timeout the flag is up and the data is void
+        tc_fence_after();
+        uint32_t v[32];
+        tc_ld32(t_lane + b * kBN, v);
+        tc_wait_ld();
+        if (MODE == DMOQ_A8) {   // re-arm the bias for the buffer's next use; completes behind the scale math
+#pragma unroll
+          for (int q = 0; q < 4; ++q) tc_st8_fill(t_lane + b * kBN + 8 * q, kMagicBits);
+        }
+        const float4* nrm4 = reinterpret_cast<const float4*>(&S.norm[slot][cq * 32]);
+        const float2 xs2 = make_float2(xs, xs);
+        const float off = (MODE == DMOQ_A8) ? -kMagicFloat * xs : 0.f;
+        const float2 off2 = make_float2(off, off);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 n4 = nrm4[q];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int j = 4 * q + 2 * h;
+            const float2 f = make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+            const float2 n2 = h ? make_float2(n4.z, n4.w) : make_float2(n4.x, n4.y);
+            // INT8: (acc_biased - M) * xs in one fma with the exact constant -M*xs; e4m3: acc * xs;
+            // fp16 / e2m1 operands: no row scale (the block scales are applied by the MMA)
+            const float2 t2 = (MODE == DMOQ_A8 || MODE == DMOQ_FP8) ? fma2(f, xs2, off2) : f;
+            total2[j >> 1] = fma2(t2, n2, total2[j >> 1]);
+          }
+        }
+        if (MODE == DMOQ_A8 && a.partials != nullptr && live) {
+          const int n_out = a.is_down ? a.hidden : 2 * a.inter;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int n = a.is_down ? nb * kBN + cq * 32 + j
+                                    : (j < 16 ? 0 : a.inter) + nb * (kBN / 2) + cq * 16 + (j & 15);
+            a.partials[((size_t)(tile.row0 + row) * n_out + n) * G + g] = (int32_t)(v[j] - kMagicBits);
+          }
+        }
+        if (MODE == DMOQ_A8) tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&S.acc_empty[b]);
+      }
+
+      // ---- tile epilogue: a thread owns 32 consecutive image columns of its row
+      if (EPI == DMOQ_EPI_SILU) {   // image columns 32*cq + [0,16) = gate, + [16,32) = up of act columns nb*64 + 16*cq + [0,16)
+        uint32_t pk[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float o[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float gate = __half2float(__float2half_rn(e ? total2[j].y : total2[j].x));
+            const float up = __half2float(__float2half_rn(e ? total2[8 + j].y : total2[8 + j].x));
+            // fast exp and reciprocal (a few fp32 ulps) ahead of the fp16 rounding: a floating-point stage
+            const float sg = __half2float(__float2half_rn(__fdividef(gate, 1.0f + __expf(-gate))));
+            o[e] = __fmul_rn(sg, up);
+          }
+          const __half2 h2 = __floats2half2_rn(o[0], o[1]);
+          pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
+        }
+        if (live) {
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.out) + (size_t)(tile.row0 + row) * a.out_stride +
+                                                nb * (kBN / 2) + cq * 16);
+          dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        }
+      } else {
+        float wgt = 0.f;
+        if (EPI == DMOQ_EPI_WEIGHTED && live) wgt = a.row_weight[tile.row0 + row];
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const __half2 h2 = __floats2half2_rn(total2[j].x, total2[j].y);   // the fp16 output
+          if (EPI == DMOQ_EPI_WEIGHTED) {   // -> bf16, times the routing weight in fp32, -> bf16
+            const float2 hf = __half22float2(h2);
+            const float2 bf = __bfloat1622float2(__floats2bfloat162_rn(hf.x, hf.y));
+            const __nv_bfloat162 o2 = __floats2bfloat162_rn(__fmul_rn(bf.x, wgt), __fmul_rn(bf.y, wgt));
+            pk[j] = *reinterpret_cast<const uint32_t*>(&o2);
+          } else {
+            pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
+          }
+        }
+        if (live) {
+          uint16_t* orow = reinterpret_cast<uint16_t*>(a.out) + (size_t)(tile.row0 + row) * a.out_stride;
+          if (a.is_down) {
+            uint4* dst = reinterpret_cast<uint4*>(orow + nb * kBN + cq * 32);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) dst[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+          } else {   // plain gate_up rows: [gate | up], each inter wide
+            uint4* dg = reinterpret_cast<uint4*>(orow + nb * (kBN / 2) + cq * 16);
+            uint4* du = reinterpret_cast<uint4*>(orow + a.inter + nb * (kBN / 2) + cq * 16);
+            dg[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            dg[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            du[0] = make_uint4(pk[8], pk[9], pk[10], pk[11]);
+            du[1] = make_uint4(pk[12], pk[13], pk[14], pk[15]);
+          }
+        }
+      }
+    }
+  } else if (warp < kMmaWarp) {
+    // =========================================================================== producer warps
+    reg_dec<kRegsProd>();
+    const int pt = tid - 32 * kEpiWarps;              // 0..127 = tile row
+    const int pw = pt >> 5;                            // producer warp = TMEM lane quarter of its scale stores
+    // bytes of one row of the code table, and of the part of it one operand step covers
+    const size_t row_bytes = (MODE == DMOQ_A16) ? (size_t)a.a_stride * 2 : (MODE == DMOQ_FP4) ? (size_t)a.a_stride / 2 : (size_t)a.a_stride;
+    const int k_bytes = (MODE == DMOQ_A16) ? (a.is_down ? a.inter : a.hidden) * 2
+                      : (MODE == DMOQ_FP4) ? (a.is_down ? a.inter : a.hidden) / 2 : (a.is_down ? a.inter : a.hidden);
+    const int sf_per_row = a.a_stride / 32;           // FP4: e8m0 bytes per table row
+
+    struct Rows {
+      int own;        // table row of tile row pt, -1 = padding
+      int sf[4];      // FP4: table rows of tile rows lane + 32q
+    };
+    auto rows_of = [&](const DmoqTile& t) {
+      Rows rw;
+      rw.own = pt < t.rows ? (a.a_row ? a.a_row[t.row0 + pt] : t.row0 + pt) : -1;
+      if (MODE == DMOQ_FP4) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int rr = lane + 32 * q;
+          rw.sf[q] = rr < t.rows ? (a.a_row ? a.a_row[t.row0 + rr] : t.row0 + rr) : -1;
+        }
+      }
+      return rw;
+    };
+
+    uint32_t it = 0, done = 0, ig = 0;    // operand steps issued / published, groups whose norms were requested
+    auto publish = [&](uint32_t j) {
+      fence_proxy_async();               // the cp.async writes of this thread, for the tensor core's reads
+      if (MODE == DMOQ_FP4) {
+        tc_wait_st();
+        tc_fence_before();
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&S.full[j % kStages]);
+    };
+
+    DmoqTile t_next = tile_of(0), t_next2 = tile_of(1);
+    Rows r_next = rows_of(t_next);
+    for (int item = 0; item < n_items; ++item) {
+      const DmoqTile tile = t_next;
+      const Rows rw = r_next;
+      t_next = t_next2;
+      t_next2 = tile_of(item + 2);
+      r_next = rows_of(t_next);
+      const int nb = (blockIdx.x + item * stride_w) % NB;
+      const int gg0 = a.is_down ? tile.rank * G : 0;                       // first image group of this item
+      const int img_row0 = a.is_down ? nb * kBN : tile.rank * 2 * a.inter + nb * kBN;
+      const uint8_t* src_row = a.a_codes + (size_t)(rw.own < 0 ? 0 : rw.own) * row_bytes;
+      for (int st = 0; st < steps_per_item; ++st, ++it) {
+        const int s = it % kStages;
+        mbar_wait(&S.empty[s], ((it / kStages) & 1) ^ 1, abort_flag);
+        if (pt == 0 && !*abort_flag) {
+          // B tile: image rows [img_row0, +128) of the step's image row group; column norms of the groups it starts
+          const int g_first = (st * GPS) / SPG;
+          const int n_groups = (SPG == 2) ? ((st & 1) ? 0 : 1) : min(GPS, G - g_first);
+          mbar_arrive_expect_tx(&S.full[s], kTileB + n_groups * kBN * 4);
+          int x, y;
+          if (MODE == DMOQ_A16) {
+            x = (st & 1) * 128;
+            y = (gg0 + (st >> 1)) * a.n_img + img_row0;
+          } else if (MODE == DMOQ_FP4) {
+            x = 0;
+            y = ((gg0 >> 1) + st) * a.n_img + img_row0;   // two groups per image row group; gg0 is even (checked on the host)
+          } else {
+            x = 0;
+            y = (gg0 + st) * a.n_img + img_row0;
+          }
+          tma_load_2d(&S.b[s][0], &tmap_b, x, y, &S.full[s]);
+          for (int j = 0; j < n_groups; ++j, ++ig)
+            bulk_g2s(&S.norm[ig % kNormRing][0], a.norm_img + (size_t)(gg0 + g_first + j) * a.n_img + img_row0, kBN * 4, &S.full[s]);
+        } else if (pt == 0) {
+          mbar_arrive(&S.full[s]);   // keep the arrival count whole after an abort
+        }
+        // A tile: this thread's row, eight 16-byte chunks of the step's 128 bytes (zero beyond the row or the tile)
+        const int col0 = st * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          cp_async16_zfill(&S.a[s][swz128(pt, c)], src_row + col0 + c * 16, rw.own >= 0 && col0 + c * 16 < k_bytes);
+        cp_async_commit();
+        if (MODE == DMOQ_FP4) {   // the rows' block scales of the step's two groups -> TMEM columns of this stage
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              w[q] = 0x7F7F7F7Fu;
+              const int g = st * 2 + j;
+              if (rw.sf[q] >= 0 && g < G)
+                w[q] = *reinterpret_cast<const uint32_t*>(a.a_scales + (size_t)rw.sf[q] * sf_per_row + g * 4);
+            }
+            tc_st4(tmem_base + ((uint32_t)(pw * 32) << 16) + kSfaCol + (s * 2 + j) * 4, w[0], w[1], w[2], w[3]);
+          }
+        }
+        if (it - done >= (uint32_t)kLag) {
+          cp_async_wait<kLag>();
+          publish(done++);
+        }
+      }
+    }
+    while (done <= it && done < it) {   // drain: everything issued must be published
+      const uint32_t pending = it - done - 1;
+      if (pending >= 1) cp_async_wait<1>(); else cp_async_wait<0>();
+      publish(done++);
+    }
+    // no bulk copy may still be in flight when the block exits (matters after an abort)
+    if (pt == 0)
+      for (uint32_t j = (it > (uint32_t)kStages ? it - kStages : 0u); j < it; ++j) mbar_wait_quiet(&S.full[j % kStages], (j / kStages) & 1);
+  } else {
+    reg_dec<kRegsMma>();
+    if (warp == kMmaWarp) {
+      // ========================================================================= MMA warp
+      constexpr uint32_t nm = ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      constexpr uint32_t idesc_i8 = (2u << 4) | (1u << 7) | (1u << 10) | nm;    // s32 accumulate, signed 8-bit operands
+      constexpr uint32_t idesc_f8 = (1u << 4) | nm;                              // f32 accumulate, e4m3 operands
+      constexpr uint32_t idesc_f16 = (1u << 4) | nm;                             // f32 accumulate, fp16 operands
+      constexpr uint32_t idesc_f4 = (1u << 7) | (1u << 10) | (1u << 23) | nm;    // e2m1 operands, ue8m0 scales, K = 64
+      uint32_t it = 0, ia = 0;
+      for (int item = 0; item < n_items; ++item) {
+        for (int st = 0; st < steps_per_item; ++st, ++it) {
+          const int s = it % kStages;
+          bool ok = mbar_wait(&S.full[s], (it / kStages) & 1, abort_flag);
+          const int n_groups = (SPG == 2) ? 1 : min(GPS, G - st * GPS);
+          // a group's first MMA needs its accumulator buffer back from the epilogue
+          if (SPG == 1 || (st & 1) == 0) {
+            for (int j = 0; j < n_groups; ++j) {
+              const uint32_t ib = ia + j;
+              ok = mbar_wait(&S.acc_empty[ib % ACC], ((ib / ACC) & 1) ^ 1, abort_flag) && ok;
+            }
+          }
+          tc_fence_after();
+          if (lane == 0 && ok) {
+            const uint64_t da = make_desc(smem_u32(&S.a[s][0]));
+            const uint64_t db = make_desc(smem_u32(&S.b[s][0]));
+            if (MODE == DMOQ_FP4) {
+              for (int j = 0; j < n_groups; ++j) {
+                const uint32_t b = (ia + j) % ACC;
+                const uint32_t sfa = tmem_base + kSfaCol + (s * 2 + j) * 4;
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {   // 64 elements = 32 bytes of K per instruction; scale bytes 2k, 2k+1
+                  const uint32_t idesc = idesc_f4 | ((uint32_t)(2 * k) << 4) | ((uint32_t)(2 * k) << 29);
+                  tc_mma_mxf4(tmem_base + b * kBN, da + 2 * (2 * j + k), db + 2 * (2 * j + k), idesc, sfa, tmem_base + kSfbCol, k > 0);
+                }
+                tc_commit(&S.acc_full[b]);
+              }
+              tc_commit(&S.empty[s]);
+            } else {
+              const uint32_t b = ia % ACC;
+              const uint32_t d = tmem_base + b * kBN;
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {  // 32 bytes of K per instruction: +2 in 16-byte units
+                if (MODE == DMOQ_A8) tc_mma<DMOQ_A8>(d, da + 2 * k, db + 2 * k, idesc_i8, 1);  // the buffer holds the bias
+                else if (MODE == DMOQ_FP8) tc_mma<DMOQ_FP8>(d, da + 2 * k, db + 2 * k, idesc_f8, k > 0);
+                else tc_mma<DMOQ_A16>(d, da + 2 * k, db + 2 * k, idesc_f16, ((st & 1) || k > 0) ? 1u : 0u);
+              }
+              tc_commit(&S.empty[s]);
+              if (SPG == 1 || (st & 1)) tc_commit(&S.acc_full[b]);
+            }
+          }
+          if (SPG == 1 || (st & 1)) ia += n_groups;
+          __syncwarp();
+        }
+      }
+    }
+  }
+
+  // ---- teardown: all roles meet here, then the allocating warp releases TMEM
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Tensor map over a weight image seen as bytes: `rows` rows of `row_bytes`, copied in boxes of 128 bytes x 128 rows.
+int make_image_map(CUtensorMap* map, const void* image, size_t rows, size_t row_bytes) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return DMOQ_EDEVICE;
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {128, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(image), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? DMOQ_OK : DMOQ_EINVAL;
+}
+
+template <int MODE, int EPI>
+int launch(const CUtensorMap& map, const ImgArgs& a, int work_cap, cudaStream_t s) {
+  static DmoqOncePerDevice once;
+  bool* configured = once.slot();
+  if (configured == nullptr) return DMOQ_EDEVICE;
+  const int bytes = (int)sizeof(Smem) + 1024;
+  if (!*configured) {
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, gemm_img_kernel<MODE, EPI>) != cudaSuccess) return DMOQ_ELAUNCH;
+    if (fa.numRegs != kRegsLaunch) return DMOQ_ELAUNCH;   // the role budgets were sized for this pool
+    if (cudaFuncSetAttribute(gemm_img_kernel<MODE, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+      return DMOQ_ELAUNCH;
+    *configured = true;
+  }
+  int grid = dmoq_sm_count();
+  if (grid > work_cap) grid = work_cap;
+  if (grid < 1) grid = 1;
+  gemm_img_kernel<MODE, EPI><<<grid, kThreads, bytes, s>>>(map, a);
+  return dmoq_launch_status();
+}
+
+template <int MODE>
+int launch_epi(const CUtensorMap& map, const ImgArgs& a, int epi, int work_cap, cudaStream_t s) {
+  switch (epi) {
+    case DMOQ_EPI_SILU: return launch<MODE, DMOQ_EPI_SILU>(map, a, work_cap, s);
+    case DMOQ_EPI_WEIGHTED: return launch<MODE, DMOQ_EPI_WEIGHTED>(map, a, work_cap, s);
+    case DMOQ_EPI_PLAIN: return launch<MODE, DMOQ_EPI_PLAIN>(map, a, work_cap, s);
+    default: return DMOQ_EINVAL;
+  }
+}
+
+}  // namespace
+
+// True when this pool/direction has a weight image the kernel above can run on.
+bool dmoq_img_supported(const dmoq_pool_t& p, int is_down, int hidden) {
+  const void* img = is_down ? p.dn_img : p.gu_img;
+  const float* nimg = is_down ? p.dn_norm_img : p.gu_norm_img;
+  if (img == nullptr || nimg == nullptr) return false;
+  if (p.inter % 128 != 0 || hidden % 128 != 0) return false;
+  if (p.mode == DMOQ_FP4 && (p.inter / 128) % 2 != 0 && is_down && p.n_members > 1) return false;   // image groups pair up
+  return true;
+}
+
+int dmoq_grouped_gemm_img(const dmoq_route_t* route, const dmoq_pool_t& p, int pool_index, int is_down, int epilogue,
+                          int hidden, const void* a_codes, const void* a_scales, int a_stride, void* out, int out_stride,
+                          int32_t* partials, cudaStream_t s) {
+  ImgArgs a{};
+  a.tiles = reinterpret_cast<const DmoqTile*>(route->tiles);
+  a.n_tiles = route->n_tiles;
+  a.a_row = is_down ? nullptr : route->a_row;
+  a.row_weight = route->sorted_weights;
+  a.pool = pool_index;
+  a.is_down = is_down;
+  a.inter = p.inter;
+  a.hidden = hidden;
+  a.norm_img = is_down ? p.dn_norm_img : p.gu_norm_img;
+  a.n_img = is_down ? hidden : p.n_members * 2 * p.inter;
+  a.a_codes = static_cast<const uint8_t*>(a_codes);
+  a.a_scales = static_cast<const uint8_t*>(a_scales);
+  a.a_stride = a_stride;
+  a.out = out;
+  a.out_stride = out_stride;
+  a.partials = partials;
+  const int e0 = is_down ? p.dn_e0 : p.gu_e0;
+  a.sfb_word = 0x01010101u * (uint32_t)((127 + e0) & 0xFF);
+  const int groups = is_down ? p.n_members * p.inter / kG : hidden / kG;
+  // image geometry: rows of 128 elements (256 bytes as fp16, 128 bytes otherwise); e2m1 rows hold two groups
+  size_t rows, row_bytes;
+  if (p.mode == DMOQ_FP4) {
+    rows = (size_t)((groups + 1) / 2) * a.n_img;
+    row_bytes = 128;
+  } else {
+    rows = (size_t)groups * a.n_img;
+    row_bytes = (p.mode == DMOQ_A16) ? 256 : 128;
+  }
+  CUtensorMap map;
+  const int rc = make_image_map(&map, is_down ? p.dn_img : p.gu_img, rows, row_bytes);
+  if (rc != DMOQ_OK) return rc;
+  const int nb = is_down ? hidden / kBN : p.inter / (kBN / 2);
+  long long cap = (long long)route->tile_cap * nb;
+  const int work_cap = cap > (1 << 30) ? (1 << 30) : (int)cap;
+  switch (p.mode) {
+    case DMOQ_A16: return launch_epi<DMOQ_A16>(map, a, epilogue, work_cap, s);
+    case DMOQ_A8: return launch_epi<DMOQ_A8>(map, a, epilogue, work_cap, s);
+    case DMOQ_FP8: return launch_epi<DMOQ_FP8>(map, a, epilogue, work_cap, s);
+    case DMOQ_FP4: return launch_epi<DMOQ_FP4>(map, a, epilogue, work_cap, s);
+    default: return DMOQ_EINVAL;
+  }
+}
+
+// Status word of this file's kernels on the current device (0 = no bounded wait ever ran out); synchronises.
+int dmoq_img_status(int* out) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_dmoq_img_status, sizeof(int)) != cudaSuccess) return DMOQ_EDEVICE;
+  *out = v;
+  return DMOQ_OK;
+}

@@ -923,11 +923,16 @@ extern "C" int dmoq_tc_profile(unsigned long long* out32, int reset) {
 }
 #endif
 
-// Device status word of the tensor-core kernels: 0 = no bounded wait has ever timed out on this device.
+int dmoq_img_status(int* out);
+
+// Device status word of the tensor-core kernels (both kernel families): 0 = no bounded wait has ever timed out on
+// this device.
 extern "C" int dmoq_tc_status(int32_t* status_host) {
   if (!status_host) return DMOQ_EINVAL;
-  int v = 0;
+  int v = 0, w = 0;
   if (cudaMemcpyFromSymbol(&v, g_dmoq_tc_status, sizeof(int)) != cudaSuccess) return DMOQ_EDEVICE;
-  *status_host = v;
+  const int rc = dmoq_img_status(&w);
+  if (rc != DMOQ_OK) return rc;
+  *status_host = v | w;
   return DMOQ_OK;
 }

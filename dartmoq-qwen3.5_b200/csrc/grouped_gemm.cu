@@ -537,6 +537,11 @@ int dmoq_grouped_gemm_tc(const dmoq_route_t* route, const dmoq_pool_t& p, int po
                          int hidden, const void* a_codes, const void* a_scales, int a_stride, void* out, int out_stride,
                          int32_t* partials, cudaStream_t s);
 
+bool dmoq_img_supported(const dmoq_pool_t& p, int is_down, int hidden);
+int dmoq_grouped_gemm_img(const dmoq_route_t* route, const dmoq_pool_t& p, int pool_index, int is_down, int epilogue,
+                          int hidden, const void* a_codes, const void* a_scales, int a_stride, void* out, int out_stride,
+                          int32_t* partials, cudaStream_t s);
+
 // DMOQ_GEMM=mma forces the warp-level MMA kernel for every pool (A/B comparisons); default picks the
 // tcgen05 kernel wherever it applies.
 static bool use_tc_path() {
@@ -565,6 +570,10 @@ extern "C" int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* p
 
   DMOQ_CHECK_ARG((is_down ? p.dn_idx : p.gu_idx) && (is_down ? p.dn_norm : p.gu_norm));
   DMOQ_CHECK_ARG(a_stride >= (is_down ? p.inter : hidden) && a_stride % kG == 0);
+  // a pool that comes with a weight image runs on the image-fed tensor-core kernel
+  if (route->tile_m == 128 && use_tc_path() && dmoq_img_supported(p, is_down, hidden))
+    return dmoq_grouped_gemm_img(route, p, pool_index, is_down, epilogue, hidden, a_codes, a_scales, a_stride, out,
+                                 out_stride, partials, static_cast<cudaStream_t>(stream));
   if (route->tile_m == 128 && use_tc_path() && dmoq_tc_supported(p, is_down, hidden))
     return dmoq_grouped_gemm_tc(route, p, pool_index, is_down, epilogue, hidden, a_codes, a_scales, a_stride, out,
                                 out_stride, partials, static_cast<cudaStream_t>(stream));

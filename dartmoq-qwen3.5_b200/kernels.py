@@ -29,6 +29,9 @@ from . import format as fmt
 from ._lib import A16, A8, FP8, FP4, EPI_PLAIN, EPI_SILU, EPI_WEIGHTED, MAX_POOLS, TILE_M, Pool, Route, check, ptr
 
 GROUP = fmt.GROUP_SIZE
+# None: the function-level GEMMs build a weight image (dmoq_expand_weights) for e2m1 pools only, as the module does
+# at load time; True / False force it for every mode / for none
+USE_WEIGHT_IMAGES = None
 
 
 def _stream():
@@ -254,6 +257,17 @@ def _merged(mode: int, is_down: bool, a_codes: torch.Tensor, a_scales: Optional[
             p.dn_idx_wide = wide.data_ptr()
         else:
             p.gu_idx_wide = wide.data_ptr()
+    use_img = (mode == FP4) if USE_WEIGHT_IMAGES is None else bool(USE_WEIGHT_IMAGES)
+    if use_img and not (mode == FP4 and bit_width == 8):
+        side = int(is_down)
+        img = torch.empty(max(int(lib.dmoq_weight_image_bytes(C.byref(p), side, hidden)), 16), dtype=torch.uint8, device=dev)
+        g_cnt_img = (n_members * inter // GROUP) if is_down else hidden // GROUP
+        nimg = torch.empty((g_cnt_img, hidden if is_down else n_members * 2 * inter), dtype=torch.float32, device=dev)
+        check(lib.dmoq_expand_weights(C.byref(p), side, hidden, ptr(img), ptr(nimg), _stream()), "dmoq_expand_weights")
+        if is_down:
+            p.dn_img, p.dn_norm_img = img.data_ptr(), nimg.data_ptr()
+        else:
+            p.gu_img, p.gu_norm_img = img.data_ptr(), nimg.data_ptr()
     out = torch.empty((n_rows, n_out), dtype=out_dtype, device=dev)
     check(lib.dmoq_grouped_gemm(C.byref(route.c), pool, 0, int(is_down), epilogue, hidden,
                                 ptr(a_codes), ptr(a_scales), a_stride, ptr(out), n_out, ptr(partials), _stream()),

@@ -219,6 +219,46 @@ class _PoolRuntime:
         c.gu_rot, c.dn_rot = self.gu_rot.data_ptr(), self.dn_rot.data_ptr()
         if self.gu_idx_wide is not None:
             c.gu_idx_wide, c.dn_idx_wide = self.gu_idx_wide.data_ptr(), self.dn_idx_wide.data_ptr()
+        # weight images (codewords looked up once, operand-row layout): sizes now, tensors on demand
+        lib = _lib.load()
+        self.img_bytes = (int(lib.dmoq_weight_image_bytes(C.byref(c), 0, hidden)),
+                          int(lib.dmoq_weight_image_bytes(C.byref(c), 1, hidden)))
+        self.norm_img = [None, None]     # fp32 column norms in image row order (kept once built)
+        self.img = [None, None]          # resident images (FP4: the load-time fold; other modes on request)
+
+    def build_norm_images(self) -> None:
+        """fp32 norms in image row order for both projections (small; kept for the life of the pool)."""
+        if self.norm_img[0] is not None:
+            return
+        lib = _lib.load()
+        dev = self.gu_idx.device
+        for side, (G, N) in enumerate(((self.hidden // GROUP, self.n_members * 2 * self.inter),
+                                       (self.n_members * self.inter // GROUP, self.hidden))):
+            nimg = torch.empty((G, N), dtype=torch.float32, device=dev)
+            scratch = torch.empty(max(self.img_bytes[side], 16), dtype=torch.uint8, device=dev)
+            check(lib.dmoq_expand_weights(C.byref(self.c), side, self.hidden, ptr(scratch), ptr(nimg), _stream()),
+                  "dmoq_expand_weights")
+            self.norm_img[side] = nimg
+        self.c.gu_norm_img, self.c.dn_norm_img = self.norm_img[0].data_ptr(), self.norm_img[1].data_ptr()
+
+    def build_resident_images(self) -> None:
+        """Both weight images kept in device memory (WxFP4: the reference's load-time fold into e2m1)."""
+        if self.img[0] is not None:
+            return
+        lib = _lib.load()
+        dev = self.gu_idx.device
+        first = self.norm_img[0] is None
+        for side in (0, 1):
+            G, N = ((self.hidden // GROUP, self.n_members * 2 * self.inter) if side == 0
+                    else (self.n_members * self.inter // GROUP, self.hidden))
+            img = torch.empty(max(self.img_bytes[side], 16), dtype=torch.uint8, device=dev)
+            nimg = torch.empty((G, N), dtype=torch.float32, device=dev) if first else None
+            check(lib.dmoq_expand_weights(C.byref(self.c), side, self.hidden, ptr(img), ptr(nimg), _stream()),
+                  "dmoq_expand_weights")
+            self.img[side] = img
+            if first:
+                self.norm_img[side] = nimg
+        self.c.gu_norm_img, self.c.dn_norm_img = self.norm_img[0].data_ptr(), self.norm_img[1].data_ptr()
 
     # bytes per activation-code row / scale row for K columns in this pool's mode
     def code_bytes(self, k: int) -> int:
@@ -320,9 +360,39 @@ class _Engine:
             if p.mode == A8:
                 return p.bit != 8 or bool(p.identity)
             return p.mode == FP8 and p.bit != 8
-        self.all_tensor_core = all(_tc(p) or p.n_members < 8 for p in self.pools)
         self._ws: Dict[int, _Workspace] = {}
         self.last_launches = 0
+        # weight images: WxFP4 pools fold their codebooks into e2m1 images at load time (as the reference does, within
+        # its byte budget); the other modes expand a pool into a transient image per forward once an expert expects
+        # enough rows to repay the expansion ("auto"), always ("always", images then stay resident) or never
+        self.weight_images = getattr(m, "weight_images", "auto")
+        self.image_min_rows = int(getattr(m, "weight_image_min_rows", 192))
+        budget = int(getattr(m, "_FOLD_BYTES_BUDGET", 16 << 30))
+        self._img_scratch = None
+        for p in self.pools:
+            want = self.weight_images != "never" and (p.mode == FP4 or self.weight_images == "always")
+            if want and sum(p.img_bytes) > 0 and sum(p.img_bytes) <= budget:
+                p.build_resident_images()
+                budget -= sum(p.img_bytes)
+        self.all_tensor_core = all(_tc(p) or p.img[0] is not None or p.n_members < 8 for p in self.pools)
+
+    def _image_scratch(self) -> torch.Tensor:
+        """One buffer for the transient image of whichever pool / projection is being computed."""
+        if self._img_scratch is None:
+            need = max(max(p.img_bytes) for p in self.pools)
+            self._img_scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=self.device)
+        return self._img_scratch
+
+    def _image_mode(self, p: "_PoolRuntime", T: int, tile_m: int) -> int:
+        """0: no image (index expansion inside the GEMM), 1: resident image, 2: transient image this forward."""
+        if tile_m != TILE_M or self.weight_images == "never":
+            return 0
+        if p.img[0] is not None:
+            return 1
+        if p.mode == FP4 or sum(p.img_bytes) == 0:
+            return 0
+        expect = T if p.shared else T * self.k_v / max(self.E_v, 1)
+        return 2 if expect >= self.image_min_rows else 0
 
     # ------------------------------------------------------------------ per-T buffers
     def workspace(self, T: int) -> _Workspace:
@@ -430,19 +500,36 @@ class _Engine:
                                         ws.caps[i], n_dev, p.c.gu_act_scale, ptr(ws.act_codes[i]),
                                         ptr(ws.act_scales[i]), s), "dmoq_rotate_quant")
         mark("rotate_quant")
+        # pool by pool: gate_up + SiLU, down-side rotation, down.  The down-side code / scale scratch and the transient
+        # weight image are shared by all pools; stream order makes each consumer finish before the next producer writes
         for i, p in enumerate(self.pools):
+            img = self._image_mode(p, T, ws.tile_m)
+            if img:
+                p.build_norm_images()
+            p.c.gu_img = p.c.dn_img = None
+            if img == 1:
+                p.c.gu_img, p.c.dn_img = p.img[0].data_ptr(), p.img[1].data_ptr()
+            scratch = self._image_scratch() if img == 2 else None
+            if img == 2:
+                check(lib.dmoq_expand_weights(C.byref(p.c), 0, self.hidden, ptr(scratch), None, s), "dmoq_expand_weights")
+                p.c.gu_img = scratch.data_ptr()
+                self.last_launches += 2
+                mark("expand_gate_up:" + p.key)
+            self.pool_array[i] = p.c
             part = None if partials is None else partials.get(("gate_up", p.key))
             check(lib.dmoq_grouped_gemm(C.byref(ws.route), self.pool_array, i, 0, EPI_SILU, self.hidden,
                                         ptr(ws.act_codes[i]), ptr(ws.act_scales[i]), self.hidden,
                                         ptr(ws.act), self.inter_max, ptr(part), s), "dmoq_grouped_gemm(gate_up)")
             mark("gate_up_silu:" + p.key)
-        # down side, pool by pool: the code / scale scratch is shared by all pools and its byte pitch
-        # depends on the pool's mode, so a pool's codes are consumed before the next pool writes its own
-        for i, p in enumerate(self.pools):
             check(lib.dmoq_rotate_quant_down(C.byref(ws.route), self.pool_array, i, ptr(ws.act), self.inter_max,
                                              ptr(ws.dn_codes), ptr(ws.dn_scales), self.inter_max, s),
                   "dmoq_rotate_quant_down")
             mark("rotate_quant_down:" + p.key)
+            if img == 2:
+                check(lib.dmoq_expand_weights(C.byref(p.c), 1, self.hidden, ptr(scratch), None, s), "dmoq_expand_weights")
+                p.c.dn_img = scratch.data_ptr()
+                self.pool_array[i] = p.c
+                mark("expand_down:" + p.key)
             part = None if partials is None else partials.get(("down", p.key))
             # plain fp16 rows; the routing weight and its bf16 rounding chain are applied by the combine, which
             # is bound by HBM and has arithmetic to spare

@@ -90,6 +90,14 @@ typedef struct dmoq_pool {
      byte permutes instead of spreading bits; when NULL these pools run on the warp-level kernel. */
   const uint8_t* gu_idx_wide;
   const uint8_t* dn_idx_wide;
+  /* optional: weight images made by dmoq_expand_weights (codewords already looked up, operand-row layout) with
+     their fp32 column norms in image row order.  When present the tensor-core GEMM reads them with TMA tensor-map
+     copies instead of expanding indices per tile.  WxFP4 images are the load-time fold of the codebook into e2m1
+     (turboquant_utils/triton_kernels_fp4.py:80). */
+  const void* gu_img;
+  const void* dn_img;
+  const float* gu_norm_img;
+  const float* dn_norm_img;
 } dmoq_pool_t;
 
 /* Routing tables produced by dmoq_route_build; all int32 unless noted. */
@@ -251,6 +259,22 @@ int dmoq_convert_group_first(const uint8_t* row_major, int32_t N, int32_t K, int
  * (G, N, 64) for dmoq_pool_t.gu_idx_wide / dn_idx_wide.
  */
 int dmoq_widen_indices(const uint8_t* packed, int64_t n_bytes, int32_t bit, uint8_t* wide, void* stream);
+
+/*
+ * Weight image of one pool and one projection (is_down 0: gate_up, 1: down) for dmoq_pool_t.gu_img / dn_img, and its
+ * fp32 column norms for gu_norm_img / dn_norm_img (norm_image may be NULL when only the codewords change).  Every
+ * codebook index is looked up in the pool's mode table once, here, instead of once per 128-row tile in the GEMM:
+ *   A8 / FP8 (G, N, 128) bytes, A16 (G, N, 128) fp16, FP4 (ceil(G/2), N, 128) bytes = two groups of packed e2m1 per
+ *   row, which is the reference's load-time fold (turboquant_utils/triton_kernels_fp4.py:80-127,
+ *   quantization/wxfp4/bit_partitioned_moe.py:98-125); the other modes have no reference counterpart (its kernels
+ *   look indices up per tile, triton_kernels_a8.py:893-902).
+ * N = n_members*2*inter with each member's gate and up rows interleaved in runs of 16 (gate_up), or hidden (down);
+ * G = hidden/128 (gate_up) or n_members*inter/128 (down).  dmoq_weight_image_bytes gives the image size;
+ * the norm image holds G*N floats.  Reads pool->{gu,dn}_{idx,norm,lut}, bit, mode, identity_lut, n_members, inter.
+ */
+size_t dmoq_weight_image_bytes(const dmoq_pool_t* pool, int32_t is_down, int32_t hidden);
+int dmoq_expand_weights(const dmoq_pool_t* pool, int32_t is_down, int32_t hidden, void* image, float* norm_image,
+                        void* stream);
 
 #ifdef __cplusplus
 }

@@ -258,9 +258,12 @@ def _close_fp16(got, want):
     assert rel_fro(got, want) < 1e-4 and (got != want).mean() < 5e-3
 
 
+@pytest.mark.parametrize("images", (False, True))
 @pytest.mark.parametrize("b", (1, 2, 4))
-def test_merged_gemm_reference_golden(golden, b):
-    """Function-level operators on the reference's own inputs: A8 bit-exact (codes, int32 sums, fp16 output)."""
+def test_merged_gemm_reference_golden(golden, b, images, monkeypatch):
+    """Function-level operators on the reference's own inputs: A8 bit-exact (codes, int32 sums, fp16 output).
+    ``images``: every mode through the image-fed tensor-core kernel (weights looked up once by dmoq_expand_weights)."""
+    monkeypatch.setattr(K, "USE_WEIGHT_IMAGES", True if images else None)
     g = golden("merged_gemm")
     H = I = 256
     gu_i, gu_n, dn_i, dn_n, rows, groups = _gemm_inputs(g, b)
@@ -349,10 +352,12 @@ def _layer(mode, seed=77, **kw):
     return synth.build_layer(**cfg)
 
 
+@pytest.mark.parametrize("images", ["auto", "always", "never"])
 @pytest.mark.parametrize("mode", ["wxa8", "wxa16", "wxfp8", "wxfp4"])
 @pytest.mark.parametrize("T", [1, 5, 150, 700])
-def test_module_forward_vs_oracle(mode, T):
+def test_module_forward_vs_oracle(mode, T, images):
     moe = _layer(mode)
+    moe.weight_images = images     # "always": every pool through the image-fed kernel; "never": index expansion per tile
     x = synth.make_activations(T, 256, seed=T)
     tw, ti, sw = routing(moe, x)
     ref = O.moe_forward(to_oracle_layer(moe), x, tw, ti, sw)
@@ -385,11 +390,13 @@ def test_module_with_logits_gate_uses_fused_router():
     assert rel_fro(y.float().cpu().numpy(), ref["y"]) < TOL["wxa8"]
 
 
+@pytest.mark.parametrize("images", ["never", "always"])
 @pytest.mark.parametrize("hoist", [True, False])
-def test_a8_stages_bit_exact(hoist):
+def test_a8_stages_bit_exact(hoist, images):
     """INT8 path, stage by stage: activation codes, stored scales and int32 group sums equal the oracle's."""
     moe = _layer("wxa8", seed=5, n_experts=6, top_k=4)
     moe.enable_rotation_hoist = hoist
+    moe.weight_images = images
     T = 90
     x = synth.make_activations(T, 256, seed=9)
     tw, ti, sw = routing(moe, x)
@@ -425,7 +432,8 @@ def test_a8_stages_bit_exact(hoist):
         same = np.all(act == st["act"].astype(np.float32), axis=1)
         dn_codes = ws.dn_codes.view(torch.int8).reshape(-1, eng.inter_max)[rows, :p.inter].cpu().numpy()
         want = np.concatenate(st["dn_codes"])
-        assert same.mean() > 0.5 and np.array_equal(dn_codes[same], want[same])
+        assert same.mean() > 0.9, f"{(~same).sum()} of {same.size} SiLU rows differ from the CPU in the last place"
+        assert np.array_equal(dn_codes[same], want[same])
         assert np.array_equal(parts[("down", p.key)][rows].cpu().numpy()[same], st["parts_dn"][same])
     assert rel_fro(y.float().cpu().numpy(), ref["y"]) < 1e-2
 

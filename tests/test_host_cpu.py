@@ -77,7 +77,7 @@ def test_capi_exports_every_declared_symbol():
 
 def test_struct_layout_matches_header():
     """ctypes mirrors have the field order and sizes of the C structs (pointers 8 bytes, ints 4)."""
-    assert ctypes.sizeof(_lib.Pool) == 6 * 4 + 6 * 8 + 3 * 4 + 2 * 4 + 4 + 4 * 8 + 2 * 8  # includes 4 bytes of padding
+    assert ctypes.sizeof(_lib.Pool) == 6 * 4 + 6 * 8 + 3 * 4 + 2 * 4 + 4 + 4 * 8 + 2 * 8 + 4 * 8  # includes 4 bytes of padding
     assert ctypes.sizeof(_lib.Route) == 6 * 4 + 12 * 8 + 4 + 4 + 8
 
 
