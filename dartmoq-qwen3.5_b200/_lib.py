@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libdmoq.so")
+# DMOQ_LIB points at another build of the same library (tuning builds); default: the in-tree one
+LIB_PATH = os.environ.get("DMOQ_LIB") or os.path.join(HERE, "libdmoq.so")
 
 MAX_POOLS = 8
 A16, A8, FP8, FP4 = 0, 1, 2, 3
@@ -71,6 +72,8 @@ EXPORTS = {
     "dmoq_combine_weighted": (C.c_int, [C.POINTER(Route), C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "dmoq_convert_group_first": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "dmoq_widen_indices": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
+    "dmoq_gather_rows": (C.c_int, [C.POINTER(Route), C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
+                                   C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "dmoq_weight_image_bytes": (C.c_size_t, [C.POINTER(Pool), C.c_int32, C.c_int32]),
     "dmoq_expand_weights": (C.c_int, [C.POINTER(Pool), C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
 }

@@ -12,6 +12,8 @@ LIB = os.path.join(HERE, "libdmoq.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC"]
+# extra compiler flags for tuning builds, e.g. DMOQ_CFLAGS="-DDMOQ_IMG_PROFILE"
+FLAGS += os.environ.get("DMOQ_CFLAGS", "").split()
 PER_FILE_FLAGS = {}
 
 

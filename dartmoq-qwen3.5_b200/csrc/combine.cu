@@ -155,6 +155,51 @@ extern "C" int dmoq_convert_group_first(const uint8_t* row_major, int32_t N, int
   return dmoq_launch_status();
 }
 
+// Rows of one pool's activation-code table gathered into routed-row order: dst row r = src row a_row[r] for every row
+// r of the pool's tiles.  One warp per row, 16-byte chunks; the few scale bytes of a row go along.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const DmoqTile* __restrict__ tiles, const int32_t* __restrict__ n_tiles,
+                                                          int pool, const int32_t* __restrict__ a_row,
+                                                          const uint8_t* __restrict__ src, int src_pitch, int row_bytes,
+                                                          uint8_t* __restrict__ dst, int dst_pitch,
+                                                          const uint8_t* __restrict__ ssrc, int ssrc_pitch, int scale_bytes,
+                                                          uint8_t* __restrict__ sdst, int sdst_pitch) {
+  const int n = n_tiles[pool];
+  const DmoqTile* mine = tiles + n_tiles[DMOQ_MAX_POOLS + pool];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  for (int t = blockIdx.x; t < n; t += gridDim.x) {
+    const DmoqTile tile = mine[t];
+    for (int r = warp; r < tile.rows; r += n_warps) {
+      const size_t to = (size_t)(tile.row0 + r), from = (size_t)a_row[tile.row0 + r];
+      for (int c = lane * 16; c < row_bytes; c += 512)
+        *reinterpret_cast<uint4*>(dst + to * dst_pitch + c) = *reinterpret_cast<const uint4*>(src + from * src_pitch + c);
+      if (ssrc != nullptr)
+        for (int c = lane * 2; c < scale_bytes; c += 64)
+          *reinterpret_cast<uint16_t*>(sdst + to * sdst_pitch + c) = *reinterpret_cast<const uint16_t*>(ssrc + from * ssrc_pitch + c);
+    }
+  }
+}
+
+extern "C" int dmoq_gather_rows(const dmoq_route_t* route, int32_t pool_index, const void* src_codes,
+                                int32_t src_pitch_bytes, int32_t row_bytes, void* dst_codes, int32_t dst_pitch_bytes,
+                                const void* src_scales, int32_t src_scale_pitch, int32_t scale_bytes, void* dst_scales,
+                                int32_t dst_scale_pitch, void* stream) {
+  DMOQ_CHECK_ARG(route && src_codes && dst_codes && route->a_row && route->tiles && route->n_tiles);
+  DMOQ_CHECK_ARG(pool_index >= 0 && pool_index < route->n_pools);
+  DMOQ_CHECK_ARG(row_bytes > 0 && row_bytes % 16 == 0 && src_pitch_bytes % 16 == 0 && dst_pitch_bytes % 16 == 0);
+  DMOQ_CHECK_ARG(src_pitch_bytes >= row_bytes && dst_pitch_bytes >= row_bytes);
+  DMOQ_CHECK_ARG((src_scales == nullptr) == (dst_scales == nullptr));
+  DMOQ_CHECK_ARG(src_scales == nullptr || (scale_bytes > 0 && scale_bytes % 2 == 0 && src_scale_pitch % 2 == 0 && dst_scale_pitch % 2 == 0));
+  int blocks = route->tile_cap;
+  const int cap = 8 * dmoq_sm_count();
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  gather_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const DmoqTile*>(route->tiles), route->n_tiles, pool_index, route->a_row,
+      static_cast<const uint8_t*>(src_codes), src_pitch_bytes, row_bytes, static_cast<uint8_t*>(dst_codes), dst_pitch_bytes,
+      static_cast<const uint8_t*>(src_scales), src_scale_pitch, scale_bytes, static_cast<uint8_t*>(dst_scales), dst_scale_pitch);
+  return dmoq_launch_status();
+}
+
 extern "C" int dmoq_version(void) { return DMOQ_VERSION; }
 
 extern "C" const char* dmoq_strerror(int code) {

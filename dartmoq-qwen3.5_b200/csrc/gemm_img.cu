@@ -14,9 +14,9 @@
 //   warps 0-15   epilogue: warp w drains lanes 32*(w%4).. of columns 32*(w/4).. of the group's accumulator
 //                (tcgen05.ld 32x32b: a thread owns one row), folds (acc * row_scale) * col_norm into an fp32 running
 //                total, and at the end of a tile writes SiLU*up / plain / weighted rows straight to global memory
-//   warps 16-19  producers: thread = tile row; gather the row's activation codes with cp.async into the swizzled A
-//                tile; thread 0 also issues the TMA copy of the B tile and the bulk copy of the group's column norms;
-//                in FP4 mode they store the rows' e8m0 block scales into TMEM (tcgen05.st) for the block-scaled MMA
+//   warp 16      loader: one thread issues, per operand step, the TMA copies of the A tile (128 rows of the sorted
+//                activation-code table) and of the B tile, and the bulk copy of the group's column norms
+//   warps 16-19  FP4 mode only: store the rows' e8m0 block scales into TMEM (tcgen05.st) for the block-scaled MMA
 //   warp 20      one thread issues tcgen05.mma: kind::i8 / f8f6f4 / f16, or kind::mxf4nvf4.block_scale (scale_vec 2X)
 //   warps 21-23  idle (setmaxnreg moves their registers to the epilogue)
 // Every mbarrier wait is bounded; on a timeout the CTA raises the device status word, stops issuing work and
@@ -28,22 +28,32 @@
 // raised when a bounded wait of this file's kernels runs out (read through dmoq_tc_status)
 __device__ int g_dmoq_img_status = 0;
 
+// Optional per-role cycle counters (block 0, first warp of each role); compiled in only for tuning builds.
+#ifdef DMOQ_IMG_PROFILE
+__device__ unsigned long long g_img_prof[32];
+#define PROF_DECL long long prof_t0 = 0, prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define PROF_BEGIN() prof_t0 = clock64()
+#define PROF_END(i) prof_acc[i] += clock64() - prof_t0
+#define PROF_FLUSH(base, cond)                                                        \
+  if ((cond) && blockIdx.x == 0 && lane == 0) {                                       \
+    for (int i_ = 0; i_ < 8; ++i_) atomicAdd(&g_img_prof[(base) + i_], (unsigned long long)prof_acc[i_]); \
+  }
+#else
+#define PROF_DECL
+#define PROF_BEGIN()
+#define PROF_END(i)
+#define PROF_FLUSH(base, cond)
+#endif
+
 namespace {
 
-constexpr int kBM = 128, kBN = 128, kG = DMOQ_GROUP;
-constexpr int kStages = 4;          // operand ring depth: one 128-row x 128-byte tile of A and of B per stage
-constexpr int kLag = 2;             // producers publish a stage this many stages after issuing its copies
-constexpr int kEpiWarps = 16, kProdWarps = 4;
-constexpr int kThreads = 32 * (kEpiWarps + kProdWarps + 4);
-constexpr int kMmaWarp = kEpiWarps + kProdWarps;
-constexpr int kNormRing = 16;       // column-norm slots; must exceed the groups in flight (2*kStages + accumulators)
-// setmaxnreg moves registers between warpgroups inside the pool the block got at launch (768 threads x 80); asking
-// for more than the pool holds blocks forever, so the launcher checks the compiled register count.
-constexpr int kRegsLaunch = 80;
-constexpr int kRegsEpi = 96, kRegsProd = 48, kRegsMma = 40;
-static_assert(32 * (kEpiWarps * kRegsEpi + kProdWarps * kRegsProd + 4 * kRegsMma) <= kRegsLaunch * kThreads,
-              "role register budgets exceed the block's register pool");
-constexpr int kTileB = kBM * 128;   // bytes of one operand tile
+constexpr int kBM = 128, kG = DMOQ_GROUP;
+#ifndef DMOQ_IMG_STAGES
+#define DMOQ_IMG_STAGES 4
+#endif
+constexpr int kStages = DMOQ_IMG_STAGES;   // operand ring depth: one 128-row x 128-byte A tile and one BN-row B tile per stage
+constexpr int kEpiWarps = 16;
+constexpr int kTileA = kBM * 128;   // bytes of one A operand tile
 constexpr uint32_t kSpinLimit = 1u << 26;
 constexpr long long kWaitCycles = 2000000000LL;
 // INT8 accumulators start from the bit pattern of 1.5*2^23: the int32 sum read back as fp32 is 12582912 + sum
@@ -51,20 +61,38 @@ constexpr long long kWaitCycles = 2000000000LL;
 constexpr uint32_t kMagicBits = 0x4B400000u;
 constexpr float kMagicFloat = 12582912.0f;
 constexpr int kTmemCols = 512;
-constexpr int kSfaCol = 384;        // FP4: three accumulators, then the scale-factor columns
+constexpr int kSfaCol = 384;        // FP4 (128-column tiles): three accumulators, then the scale-factor columns
 constexpr int kSfbCol = kSfaCol + kStages * 2 * 4;
+
+// Tile width and role layout.  BN = 256 (fp16 / INT8 / e4m3 operands): one tcgen05.mma covers 256 columns, so the A
+// tile is read from shared memory once per 256 columns and an item's fixed costs are halved; two 256-column
+// accumulators fill TMEM; 640 threads (16 epilogue warps, loader warp 16, MMA warp 17).  BN = 128: three
+// accumulators + the FP4 scale-factor columns; 768 threads (loader / scale warps 16-19, MMA warp 20).
+// setmaxnreg moves registers between warpgroups inside the pool the block got at launch (threads x kRegsLaunch);
+// asking for more than the pool holds blocks forever, so the launcher checks the compiled register count.
+template <int BN>
+struct Cfg {
+  static constexpr int kAuxWarps = (BN == 256) ? 4 : 8;                 // warps after the epilogue warps
+  static constexpr int kThreads = 32 * (kEpiWarps + kAuxWarps);
+  static constexpr int kMmaWarp = (BN == 256) ? kEpiWarps + 1 : kEpiWarps + 4;
+  static constexpr int kRegsLaunch = (BN == 256) ? 96 : 80;
+  static constexpr int kRegsEpi = (BN == 256) ? 112 : 96;
+  static constexpr int kRegsAux = (BN == 256) ? 32 : 40;
+  static constexpr int kNormRing = (BN == 256) ? 8 : 16;                // column-norm slots; exceeds the groups in flight
+  static constexpr int kTileB = BN * 128;
+  static_assert(32 * (kEpiWarps * kRegsEpi + kAuxWarps * kRegsAux) <= kRegsLaunch * kThreads,
+                "role register budgets exceed the block's register pool");
+};
 
 struct ImgArgs {
   const DmoqTile* tiles;
   const int32_t* n_tiles;
-  const int32_t* a_row;       // gather map (gate_up) or null (down: the row's own index)
   const float* row_weight;
   int pool, is_down, inter, hidden;
   const float* norm_img;      // (groups, n_img) fp32, image row order
   int n_img;                  // image rows per group
-  const uint8_t* a_codes;
-  const uint8_t* a_scales;    // A8/FP8: fp16 (rows, K/128); FP4: e8m0 bytes (rows, K/32)
-  int a_stride;               // row pitch of the code table in elements
+  const uint8_t* a_scales;    // A8/FP8: fp16 (rows, K/128); FP4: e8m0 bytes (rows, K/32); row r of the table feeds row r
+  int a_stride;               // row pitch of the code table in elements (the codes themselves come through tmap_a)
   void* out;
   int out_stride;
   int32_t* partials;
@@ -177,18 +205,13 @@ __device__ __forceinline__ void tc_mma_mxf4(uint32_t d_tmem, uint64_t a_desc, ui
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
       : "memory");
 }
-// 32 lanes x 32 columns: thread t of the warp receives lane base + t, register j = column base + j
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
+// accumulator loads: thread t of the warp receives lane base + t, register j = column base + j
+// 32 lanes x 8 columns
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -211,10 +234,11 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
+template <int BN>
 struct Smem {
-  uint8_t a[kStages][kTileB];   // 1024-byte aligned operand tiles
-  uint8_t b[kStages][kTileB];
-  float norm[kNormRing][kBN];   // column norms of a group, image column order
+  uint8_t a[kStages][kTileA];              // 1024-byte aligned operand tiles
+  uint8_t b[kStages][Cfg<BN>::kTileB];
+  float norm[Cfg<BN>::kNormRing][BN];      // column norms of a group, image column order
   uint64_t full[kStages], empty[kStages], acc_full[4], acc_empty[4];
   uint32_t tmem_base;
   int abort_flag;
@@ -225,27 +249,34 @@ __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.al
 template <int N>
 __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
-// Per mode: bytes of an activation element in the A tile, operand steps per group / groups per operand step.
-//   A8, FP8: one 128-byte step per group.  A16: two steps per group (64 fp16 columns each).
+// Per mode: operand steps per group / groups per operand step (a step = 128 bytes of every operand row).
+//   A8, FP8: one step per group.  A16: two steps per group (64 fp16 columns each).
 //   FP4: one step carries two groups (64 bytes of packed e2m1 each).
 template <int MODE>
 struct Shape {
   static constexpr int SPG = (MODE == DMOQ_A16) ? 2 : 1;   // operand steps per group
   static constexpr int GPS = (MODE == DMOQ_FP4) ? 2 : 1;   // groups per operand step
-  static constexpr int ACC = (MODE == DMOQ_FP4) ? 3 : 4;   // accumulator buffers
 };
 
-template <int MODE, int EPI>
-__global__ void __launch_bounds__(kThreads, 1) gemm_img_kernel(const __grid_constant__ CUtensorMap tmap_b, ImgArgs a) {
+template <int MODE, int EPI, int BN>
+__global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                                        const __grid_constant__ CUtensorMap tmap_b, ImgArgs a) {
+  using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
-  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Smem<BN>& S = *reinterpret_cast<Smem<BN>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   volatile int* abort_flag = &S.abort_flag;
-  constexpr int SPG = Shape<MODE>::SPG, GPS = Shape<MODE>::GPS, ACC = Shape<MODE>::ACC;
+  constexpr int SPG = Shape<MODE>::SPG, GPS = Shape<MODE>::GPS;
+  constexpr int ACC = (BN == 256) ? 2 : (MODE == DMOQ_FP4 ? 3 : 4);   // accumulator buffers in TMEM
+  constexpr int NH = BN / 128;                                        // 32-column blocks per epilogue thread
+  constexpr int CW = 8;                                               // accumulator columns per TMEM load
+  constexpr int NCH = 32 * NH / CW;                                   // loads per group and thread (even)
+  constexpr int kMmaWarp = C::kMmaWarp, kNormRing = C::kNormRing;
+  static_assert(!(MODE == DMOQ_FP4 && BN != 128), "the FP4 scale-factor columns need 128-column tiles");
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&S.full[s], kProdWarps + 1);   // four producer warps + the thread that announces the bulk bytes
+      mbar_init(&S.full[s], MODE == DMOQ_FP4 ? 5 : 1);   // the thread that announces the bulk bytes (+ four scale warps)
       mbar_init(&S.empty[s], 1);
     }
     for (int b = 0; b < 4; ++b) {
@@ -266,11 +297,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_img_kernel(const __grid_cons
   if (MODE == DMOQ_A8 || MODE == DMOQ_FP4) {
     if (warp < kEpiWarps) {
       const uint32_t t0 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-      if (MODE == DMOQ_A8) {   // bias every accumulator buffer: this warp's 32 lanes x 32 columns of each
+      if (MODE == DMOQ_A8) {   // bias every accumulator buffer: this warp's 32 lanes x its columns of each
 #pragma unroll
         for (int b = 0; b < ACC; ++b)
 #pragma unroll
-          for (int q = 0; q < 4; ++q) tc_st8_fill(t0 + b * kBN + (warp >> 2) * 32 + 8 * q, kMagicBits);
+          for (int q = 0; q < 4 * NH; ++q) tc_st8_fill(t0 + b * BN + (warp >> 2) * (32 * NH) + 8 * q, kMagicBits);
       } else if (warp < 4) {   // the constant weight block scale, for every column and every 32-block of K
         tc_st4(t0 + kSfbCol, a.sfb_word, a.sfb_word, a.sfb_word, a.sfb_word);
       }
@@ -283,7 +314,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_img_kernel(const __grid_cons
 
   const int n_tiles = a.n_tiles[a.pool];
   const DmoqTile* tiles = a.tiles + a.n_tiles[DMOQ_MAX_POOLS + a.pool];
-  const int NB = a.is_down ? a.hidden / kBN : a.inter / (kBN / 2);
+  const int NB = a.is_down ? a.hidden / BN : a.inter / (BN / 2);
   const int G = a.is_down ? a.inter / kG : a.hidden / kG;
   const int steps_per_item = (G * SPG + GPS - 1) / GPS;
   const int n_work = n_tiles * NB;
@@ -297,257 +328,298 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_img_kernel(const __grid_cons
 
   if (warp < kEpiWarps) {
     // =========================================================================== epilogue warps
-    reg_inc<kRegsEpi>();
+    reg_inc<C::kRegsEpi>();
     const int lq = warp & 3, cq = warp >> 2;
     const int row = lq * 32 + lane;                  // tile row of this thread
-    const uint32_t t_lane = tmem_base + ((uint32_t)(lq * 32) << 16) + cq * 32;
+    const int cbase = cq * (32 * NH);                // first of this thread's 32*NH tile columns
+    const uint32_t t_lane = tmem_base + ((uint32_t)(lq * 32) << 16) + cbase;
     const int xs_per_row = a.a_stride / kG;
     uint32_t ia = 0;                                 // groups consumed so far
+    uint32_t v[2][8];                                // accumulator chunks: one in the scale math, one in flight
+    bool prefetched = false;                         // the upcoming group's first chunk is already on its way
     DmoqTile next = tile_of(0);
+    PROF_DECL;
+#ifdef DMOQ_IMG_PROFILE
+    const long long prof_start = clock64();
+#endif
     for (int item = 0; item < n_items; ++item) {
       const DmoqTile tile = next;
       next = tile_of(item + 1);
       const int nb = (blockIdx.x + item * stride_w) % NB;
       const bool live = row < tile.rows;
-      const __half* xs_row = nullptr;
-      if (MODE == DMOQ_A8 || MODE == DMOQ_FP8) {
-        const int src = live ? (a.a_row ? a.a_row[tile.row0 + row] : tile.row0 + row) : 0;
-        xs_row = reinterpret_cast<const __half*>(a.a_scales) + (size_t)src * xs_per_row;
-      }
-      float2 total2[16];
+      // row scales: this row's G fp16 values, fetched four at a time (8-byte loads, one block ahead) where the row
+      // pitch allows, else one at a time
+      const bool has_xs = (MODE == DMOQ_A8 || MODE == DMOQ_FP8);
+      const __half* xs_row = reinterpret_cast<const __half*>(a.a_scales) + (size_t)(tile.row0 + (live ? row : 0)) * xs_per_row;
+      const bool xs_vec = (xs_per_row & 3) == 0;
+      float2 total2[16 * NH];   // pair p = this thread's columns 2p, 2p+1
 #pragma unroll
-      for (int c = 0; c < 16; ++c) total2[c] = make_float2(0.f, 0.f);
-      float xs_next = (xs_row != nullptr && live) ? __half2float(xs_row[0]) : 0.f;
+      for (int c = 0; c < 16 * NH; ++c) total2[c] = make_float2(0.f, 0.f);
+      uint2 xq = make_uint2(0u, 0u), xq_next = make_uint2(0u, 0u);
+      float xs_next = 0.f;
+      if (has_xs) {
+        if (xs_vec) xq_next = *reinterpret_cast<const uint2*>(xs_row);
+        else xs_next = __half2float(xs_row[0]);
+      }
+      int held = -1;     // accumulator buffer whose release is still owed (its bias stores are in flight)
+      auto release = [&]() {
+        if (held >= 0) {
+          if (MODE == DMOQ_A8) tc_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&S.acc_empty[held]);
+          held = -1;
+        }
+      };
 
       for (int g = 0; g < G; ++g, ++ia) {
         const uint32_t b = ia % ACC, ph = (ia / ACC) & 1;
         const uint32_t slot = ia % kNormRing;
-        const float xs = xs_next;
-        if (xs_row != nullptr && live && g + 1 < G) xs_next = __half2float(xs_row[g + 1]);   // in flight during this group
+        float xs = 0.f;
+        if (has_xs) {
+          if (xs_vec) {
+            if ((g & 3) == 0) {
+              xq = xq_next;
+              if (g + 4 < G) xq_next = *reinterpret_cast<const uint2*>(xs_row + g + 4);   // in flight during these groups
+            }
+            const uint32_t w = (g & 2) ? xq.y : xq.x;
+            xs = __half2float(__ushort_as_half((unsigned short)((g & 1) ? (w >> 16) : (w & 0xFFFFu))));
+          } else {
+            xs = xs_next;
+            if (g + 1 < G) xs_next = __half2float(xs_row[g + 1]);
+          }
+        }
         // The group's norms were bulk-copied before its operand stage completed; the MMA thread saw that completion
         // before it committed acc_full[], so they are visible here.
-        mbar_wait(&S.acc_full[b], ph, abort_flag);   // on a timeout the flag is up and the data is void
-        tc_fence_after();
-        uint32_t v[32];
-        tc_ld32(t_lane + b * kBN, v);
-        tc_wait_ld();
-        if (MODE == DMOQ_A8) {   // re-arm the bias for the buffer's next use; completes behind the scale math
-#pragma unroll
-          for (int q = 0; q < 4; ++q) tc_st8_fill(t_lane + b * kBN + 8 * q, kMagicBits);
+        if (!prefetched) {
+          PROF_BEGIN();
+          mbar_wait(&S.acc_full[b], ph, abort_flag);   // on a timeout the flag is up and the data is void
+          PROF_END(0);
+          tc_fence_after();
+          tc_ld8(t_lane + b * BN, v[0]);
         }
-        const float4* nrm4 = reinterpret_cast<const float4*>(&S.norm[slot][cq * 32]);
+        prefetched = false;
+        PROF_BEGIN();
         const float2 xs2 = make_float2(xs, xs);
         const float off = (MODE == DMOQ_A8) ? -kMagicFloat * xs : 0.f;
         const float2 off2 = make_float2(off, off);
+        // The thread's 32*NH columns in chunks of eight: the load of chunk c+1 (at the end of a group: of the next
+        // group's first chunk, if that group is ready) is in flight while chunk c goes through the scale math.
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const float4 n4 = nrm4[q];
+        for (int c = 0; c < NCH; ++c) {
+          tc_wait_ld();
+          // the previous group's buffer goes back to the MMA thread here: its bias stores were issued a whole group
+          // ago, so waiting for them costs nothing now
+          if (c == 0) release();
+          if (c + 1 < NCH) {
+            tc_ld8(t_lane + b * BN + CW * (c + 1), v[(c + 1) & 1]);
+          } else if (g + 1 < G || item + 1 < n_items) {
+            const uint32_t bn_ = (ia + 1) % ACC, phn = ((ia + 1) / ACC) & 1;
+            if (mbar_try_wait(&S.acc_full[bn_], phn)) {
+              tc_fence_after();
+              tc_ld8(t_lane + bn_ * BN, v[(c + 1) & 1]);
+              prefetched = true;
+            }
+          }
+          if (MODE == DMOQ_A8) tc_st8_fill(t_lane + b * BN + CW * c, kMagicBits);   // re-arm the bias for the buffer's next use
+          const uint32_t(&vc)[8] = v[c & 1];
+          const float4* nrm4 = reinterpret_cast<const float4*>(&S.norm[slot][cbase + CW * c]);
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int j = 4 * q + 2 * h;
-            const float2 f = make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-            const float2 n2 = h ? make_float2(n4.z, n4.w) : make_float2(n4.x, n4.y);
-            // INT8: (acc_biased - M) * xs in one fma with the exact constant -M*xs; e4m3: acc * xs;
-            // fp16 / e2m1 operands: no row scale (the block scales are applied by the MMA)
-            const float2 t2 = (MODE == DMOQ_A8 || MODE == DMOQ_FP8) ? fma2(f, xs2, off2) : f;
-            total2[j >> 1] = fma2(t2, n2, total2[j >> 1]);
+          for (int q = 0; q < 2; ++q) {
+            const float4 n4 = nrm4[q];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int j = 4 * q + 2 * e;
+              const float2 f = make_float2(__uint_as_float(vc[j]), __uint_as_float(vc[j + 1]));
+              const float2 n2 = e ? make_float2(n4.z, n4.w) : make_float2(n4.x, n4.y);
+              // INT8: (acc_biased - M) * xs in one fma with the exact constant -M*xs; e4m3: acc * xs;
+              // fp16 / e2m1 operands: no row scale (the block scales are applied by the MMA)
+              const float2 t2 = (MODE == DMOQ_A8 || MODE == DMOQ_FP8) ? fma2(f, xs2, off2) : f;
+              total2[(CW * c + j) >> 1] = fma2(t2, n2, total2[(CW * c + j) >> 1]);
+            }
+          }
+          if (BN == 128 && MODE == DMOQ_A8 && a.partials != nullptr && live) {   // parity checks only (128-column tiles)
+            const int n_out = a.is_down ? a.hidden : 2 * a.inter;
+#pragma unroll
+            for (int j = 0; j < CW; ++j) {
+              const int col = CW * c + j;                                        // 0..31
+              const int n = a.is_down ? nb * BN + cbase + col
+                                      : (col < 16 ? 0 : a.inter) + nb * (BN / 2) + cq * 16 + (col & 15);
+              a.partials[((size_t)(tile.row0 + row) * n_out + n) * G + g] = (int32_t)(vc[j] - kMagicBits);
+            }
           }
         }
-        if (MODE == DMOQ_A8 && a.partials != nullptr && live) {
-          const int n_out = a.is_down ? a.hidden : 2 * a.inter;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int n = a.is_down ? nb * kBN + cq * 32 + j
-                                    : (j < 16 ? 0 : a.inter) + nb * (kBN / 2) + cq * 16 + (j & 15);
-            a.partials[((size_t)(tile.row0 + row) * n_out + n) * G + g] = (int32_t)(v[j] - kMagicBits);
-          }
-        }
-        if (MODE == DMOQ_A8) tc_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&S.acc_empty[b]);
+        PROF_END(2);
+        held = (int)b;
       }
+      release();   // before the tile's output stores: the MMA thread may run ahead into the next item
+      PROF_BEGIN();
 
-      // ---- tile epilogue: a thread owns 32 consecutive image columns of its row
-      if (EPI == DMOQ_EPI_SILU) {   // image columns 32*cq + [0,16) = gate, + [16,32) = up of act columns nb*64 + 16*cq + [0,16)
-        uint32_t pk[8];
+      // ---- tile epilogue: a thread owns 32*NH consecutive image columns of its row
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float o[2];
+      for (int h = 0; h < NH; ++h) {
+        if (EPI == DMOQ_EPI_SILU) {   // image columns [0,16) of the block = gate, [16,32) = up of 16 consecutive outputs
+          uint32_t pk[8];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const float gate = __half2float(__float2half_rn(e ? total2[j].y : total2[j].x));
-            const float up = __half2float(__float2half_rn(e ? total2[8 + j].y : total2[8 + j].x));
-            // fast exp and reciprocal (a few fp32 ulps) ahead of the fp16 rounding: a floating-point stage
-            const float sg = __half2float(__float2half_rn(__fdividef(gate, 1.0f + __expf(-gate))));
-            o[e] = __fmul_rn(sg, up);
-          }
-          const __half2 h2 = __floats2half2_rn(o[0], o[1]);
-          pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
-        }
-        if (live) {
-          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.out) + (size_t)(tile.row0 + row) * a.out_stride +
-                                                nb * (kBN / 2) + cq * 16);
-          dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-          dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-        }
-      } else {
-        float wgt = 0.f;
-        if (EPI == DMOQ_EPI_WEIGHTED && live) wgt = a.row_weight[tile.row0 + row];
-        uint32_t pk[16];
+          for (int j = 0; j < 8; ++j) {
+            float o[2];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const __half2 h2 = __floats2half2_rn(total2[j].x, total2[j].y);   // the fp16 output
-          if (EPI == DMOQ_EPI_WEIGHTED) {   // -> bf16, times the routing weight in fp32, -> bf16
-            const float2 hf = __half22float2(h2);
-            const float2 bf = __bfloat1622float2(__floats2bfloat162_rn(hf.x, hf.y));
-            const __nv_bfloat162 o2 = __floats2bfloat162_rn(__fmul_rn(bf.x, wgt), __fmul_rn(bf.y, wgt));
-            pk[j] = *reinterpret_cast<const uint32_t*>(&o2);
-          } else {
+            for (int e = 0; e < 2; ++e) {
+              const float gate = __half2float(__float2half_rn(e ? total2[16 * h + j].y : total2[16 * h + j].x));
+              const float up = __half2float(__float2half_rn(e ? total2[16 * h + 8 + j].y : total2[16 * h + 8 + j].x));
+              // fast exp and reciprocal (a few fp32 ulps) ahead of the fp16 rounding: a floating-point stage
+              const float sg = __half2float(__float2half_rn(__fdividef(gate, 1.0f + __expf(-gate))));
+              o[e] = __fmul_rn(sg, up);
+            }
+            const __half2 h2 = __floats2half2_rn(o[0], o[1]);
             pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
           }
-        }
-        if (live) {
-          uint16_t* orow = reinterpret_cast<uint16_t*>(a.out) + (size_t)(tile.row0 + row) * a.out_stride;
-          if (a.is_down) {
-            uint4* dst = reinterpret_cast<uint4*>(orow + nb * kBN + cq * 32);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) dst[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-          } else {   // plain gate_up rows: [gate | up], each inter wide
-            uint4* dg = reinterpret_cast<uint4*>(orow + nb * (kBN / 2) + cq * 16);
-            uint4* du = reinterpret_cast<uint4*>(orow + a.inter + nb * (kBN / 2) + cq * 16);
-            dg[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            dg[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-            du[0] = make_uint4(pk[8], pk[9], pk[10], pk[11]);
-            du[1] = make_uint4(pk[12], pk[13], pk[14], pk[15]);
+          if (live) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.out) + (size_t)(tile.row0 + row) * a.out_stride +
+                                                  nb * (BN / 2) + (cq * NH + h) * 16);
+            dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
           }
-        }
-      }
-    }
-  } else if (warp < kMmaWarp) {
-    // =========================================================================== producer warps
-    reg_dec<kRegsProd>();
-    const int pt = tid - 32 * kEpiWarps;              // 0..127 = tile row
-    const int pw = pt >> 5;                            // producer warp = TMEM lane quarter of its scale stores
-    // bytes of one row of the code table, and of the part of it one operand step covers
-    const size_t row_bytes = (MODE == DMOQ_A16) ? (size_t)a.a_stride * 2 : (MODE == DMOQ_FP4) ? (size_t)a.a_stride / 2 : (size_t)a.a_stride;
-    const int k_bytes = (MODE == DMOQ_A16) ? (a.is_down ? a.inter : a.hidden) * 2
-                      : (MODE == DMOQ_FP4) ? (a.is_down ? a.inter : a.hidden) / 2 : (a.is_down ? a.inter : a.hidden);
-    const int sf_per_row = a.a_stride / 32;           // FP4: e8m0 bytes per table row
-
-    struct Rows {
-      int own;        // table row of tile row pt, -1 = padding
-      int sf[4];      // FP4: table rows of tile rows lane + 32q
-    };
-    auto rows_of = [&](const DmoqTile& t) {
-      Rows rw;
-      rw.own = pt < t.rows ? (a.a_row ? a.a_row[t.row0 + pt] : t.row0 + pt) : -1;
-      if (MODE == DMOQ_FP4) {
+        } else {
+          float wgt = 0.f;
+          if (EPI == DMOQ_EPI_WEIGHTED && live) wgt = a.row_weight[tile.row0 + row];
+          uint32_t pk[16];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int rr = lane + 32 * q;
-          rw.sf[q] = rr < t.rows ? (a.a_row ? a.a_row[t.row0 + rr] : t.row0 + rr) : -1;
-        }
-      }
-      return rw;
-    };
-
-    uint32_t it = 0, done = 0, ig = 0;    // operand steps issued / published, groups whose norms were requested
-    auto publish = [&](uint32_t j) {
-      fence_proxy_async();               // the cp.async writes of this thread, for the tensor core's reads
-      if (MODE == DMOQ_FP4) {
-        tc_wait_st();
-        tc_fence_before();
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&S.full[j % kStages]);
-    };
-
-    DmoqTile t_next = tile_of(0), t_next2 = tile_of(1);
-    Rows r_next = rows_of(t_next);
-    for (int item = 0; item < n_items; ++item) {
-      const DmoqTile tile = t_next;
-      const Rows rw = r_next;
-      t_next = t_next2;
-      t_next2 = tile_of(item + 2);
-      r_next = rows_of(t_next);
-      const int nb = (blockIdx.x + item * stride_w) % NB;
-      const int gg0 = a.is_down ? tile.rank * G : 0;                       // first image group of this item
-      const int img_row0 = a.is_down ? nb * kBN : tile.rank * 2 * a.inter + nb * kBN;
-      const uint8_t* src_row = a.a_codes + (size_t)(rw.own < 0 ? 0 : rw.own) * row_bytes;
-      for (int st = 0; st < steps_per_item; ++st, ++it) {
-        const int s = it % kStages;
-        mbar_wait(&S.empty[s], ((it / kStages) & 1) ^ 1, abort_flag);
-        if (pt == 0 && !*abort_flag) {
-          // B tile: image rows [img_row0, +128) of the step's image row group; column norms of the groups it starts
-          const int g_first = (st * GPS) / SPG;
-          const int n_groups = (SPG == 2) ? ((st & 1) ? 0 : 1) : min(GPS, G - g_first);
-          mbar_arrive_expect_tx(&S.full[s], kTileB + n_groups * kBN * 4);
-          int x, y;
-          if (MODE == DMOQ_A16) {
-            x = (st & 1) * 128;
-            y = (gg0 + (st >> 1)) * a.n_img + img_row0;
-          } else if (MODE == DMOQ_FP4) {
-            x = 0;
-            y = ((gg0 >> 1) + st) * a.n_img + img_row0;   // two groups per image row group; gg0 is even (checked on the host)
-          } else {
-            x = 0;
-            y = (gg0 + st) * a.n_img + img_row0;
-          }
-          tma_load_2d(&S.b[s][0], &tmap_b, x, y, &S.full[s]);
-          for (int j = 0; j < n_groups; ++j, ++ig)
-            bulk_g2s(&S.norm[ig % kNormRing][0], a.norm_img + (size_t)(gg0 + g_first + j) * a.n_img + img_row0, kBN * 4, &S.full[s]);
-        } else if (pt == 0) {
-          mbar_arrive(&S.full[s]);   // keep the arrival count whole after an abort
-        }
-        // A tile: this thread's row, eight 16-byte chunks of the step's 128 bytes (zero beyond the row or the tile)
-        const int col0 = st * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          cp_async16_zfill(&S.a[s][swz128(pt, c)], src_row + col0 + c * 16, rw.own >= 0 && col0 + c * 16 < k_bytes);
-        cp_async_commit();
-        if (MODE == DMOQ_FP4) {   // the rows' block scales of the step's two groups -> TMEM columns of this stage
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            uint32_t w[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              w[q] = 0x7F7F7F7Fu;
-              const int g = st * 2 + j;
-              if (rw.sf[q] >= 0 && g < G)
-                w[q] = *reinterpret_cast<const uint32_t*>(a.a_scales + (size_t)rw.sf[q] * sf_per_row + g * 4);
+          for (int j = 0; j < 16; ++j) {
+            const __half2 h2 = __floats2half2_rn(total2[16 * h + j].x, total2[16 * h + j].y);   // the fp16 output
+            if (EPI == DMOQ_EPI_WEIGHTED) {   // -> bf16, times the routing weight in fp32, -> bf16
+              const float2 hf = __half22float2(h2);
+              const float2 bf = __bfloat1622float2(__floats2bfloat162_rn(hf.x, hf.y));
+              const __nv_bfloat162 o2 = __floats2bfloat162_rn(__fmul_rn(bf.x, wgt), __fmul_rn(bf.y, wgt));
+              pk[j] = *reinterpret_cast<const uint32_t*>(&o2);
+            } else {
+              pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
             }
-            tc_st4(tmem_base + ((uint32_t)(pw * 32) << 16) + kSfaCol + (s * 2 + j) * 4, w[0], w[1], w[2], w[3]);
+          }
+          if (live) {
+            uint16_t* orow = reinterpret_cast<uint16_t*>(a.out) + (size_t)(tile.row0 + row) * a.out_stride;
+            if (a.is_down) {
+              uint4* dst = reinterpret_cast<uint4*>(orow + nb * BN + cbase + 32 * h);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) dst[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+            } else {   // plain gate_up rows: [gate | up], each inter wide
+              uint4* dg = reinterpret_cast<uint4*>(orow + nb * (BN / 2) + (cq * NH + h) * 16);
+              uint4* du = reinterpret_cast<uint4*>(orow + a.inter + nb * (BN / 2) + (cq * NH + h) * 16);
+              dg[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              dg[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+              du[0] = make_uint4(pk[8], pk[9], pk[10], pk[11]);
+              du[1] = make_uint4(pk[12], pk[13], pk[14], pk[15]);
+            }
           }
         }
-        if (it - done >= (uint32_t)kLag) {
-          cp_async_wait<kLag>();
-          publish(done++);
+      }
+      PROF_END(4);
+    }
+#ifdef DMOQ_IMG_PROFILE
+    prof_acc[7] = clock64() - prof_start;
+#endif
+    PROF_FLUSH(0, warp == 0);
+  } else {
+    reg_dec<C::kRegsAux>();
+    const int pw = warp - kEpiWarps;                  // FP4: 0..3 = TMEM lane quarter of the warp's scale stores
+    const bool scale_warp = (MODE == DMOQ_FP4) && pw < 4;
+    if (warp == kEpiWarps || scale_warp) {
+      // ========================================================================= loader (and FP4 scale) warps
+      const bool loader = (warp == kEpiWarps && lane == 0);
+      const int sf_per_row = a.a_stride / 32;           // FP4: e8m0 bytes per table row
+      uint32_t it = 0, ig = 0;                        // operand steps issued, groups whose norms were requested
+      PROF_DECL;
+#ifdef DMOQ_IMG_PROFILE
+      const long long prof_start = clock64();
+#endif
+      DmoqTile t_next = tile_of(0);
+      for (int item = 0; item < n_items; ++item) {
+        const DmoqTile tile = t_next;
+        t_next = tile_of(item + 1);
+        const int nb = (blockIdx.x + item * stride_w) % NB;
+        const int gg0 = a.is_down ? tile.rank * G : 0;                       // first image group of this item
+        const int img_row0 = a.is_down ? nb * BN : tile.rank * 2 * a.inter + nb * BN;
+        for (int st = 0; st < steps_per_item; ++st, ++it) {
+          const int s = it % kStages;
+          PROF_BEGIN();
+          mbar_wait(&S.empty[s], ((it / kStages) & 1) ^ 1, abort_flag);
+          PROF_END(0);
+          PROF_BEGIN();
+          if (loader) {
+            if (!*abort_flag) {
+              // A tile: rows [row0, +128) of the sorted code table, 128 bytes of the step; B tile: image rows
+              // [img_row0, +BN) of the step's image row group; column norms of the groups the step starts
+              const int g_first = (st * GPS) / SPG;
+              const int n_groups = (SPG == 2) ? ((st & 1) ? 0 : 1) : min(GPS, G - g_first);
+              mbar_arrive_expect_tx(&S.full[s], kTileA + C::kTileB + n_groups * BN * 4);
+              int x, y;
+              if (MODE == DMOQ_A16) {
+                x = (st & 1) * 128;
+                y = (gg0 + (st >> 1)) * a.n_img + img_row0;
+              } else if (MODE == DMOQ_FP4) {
+                x = 0;
+                y = ((gg0 >> 1) + st) * a.n_img + img_row0;   // two groups per image row group; gg0 is even (checked on the host)
+              } else {
+                x = 0;
+                y = (gg0 + st) * a.n_img + img_row0;
+              }
+              tma_load_2d(&S.a[s][0], &tmap_a, st * 128, tile.row0, &S.full[s]);
+              tma_load_2d(&S.b[s][0], &tmap_b, x, y, &S.full[s]);
+              for (int j = 0; j < n_groups; ++j, ++ig)
+                bulk_g2s(&S.norm[ig % kNormRing][0], a.norm_img + (size_t)(gg0 + g_first + j) * a.n_img + img_row0, BN * 4, &S.full[s]);
+            } else {
+              mbar_arrive(&S.full[s]);   // keep the arrival count whole after an abort
+            }
+          }
+          PROF_END(1);
+          if (MODE == DMOQ_FP4) {   // the rows' block scales of the step's two groups -> TMEM columns of this stage
+            PROF_BEGIN();
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              uint32_t w[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                w[q] = 0x7F7F7F7Fu;
+                const int g = st * 2 + j, rr = lane + 32 * q;
+                if (rr < tile.rows && g < G)
+                  w[q] = *reinterpret_cast<const uint32_t*>(a.a_scales + (size_t)(tile.row0 + rr) * sf_per_row + g * 4);
+              }
+              tc_st4(tmem_base + ((uint32_t)(pw * 32) << 16) + kSfaCol + (s * 2 + j) * 4, w[0], w[1], w[2], w[3]);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&S.full[s]);
+            PROF_END(2);
+          }
         }
       }
-    }
-    while (done <= it && done < it) {   // drain: everything issued must be published
-      const uint32_t pending = it - done - 1;
-      if (pending >= 1) cp_async_wait<1>(); else cp_async_wait<0>();
-      publish(done++);
-    }
-    // no bulk copy may still be in flight when the block exits (matters after an abort)
-    if (pt == 0)
-      for (uint32_t j = (it > (uint32_t)kStages ? it - kStages : 0u); j < it; ++j) mbar_wait_quiet(&S.full[j % kStages], (j / kStages) & 1);
-  } else {
-    reg_dec<kRegsMma>();
-    if (warp == kMmaWarp) {
+#ifdef DMOQ_IMG_PROFILE
+      prof_acc[7] = clock64() - prof_start;
+#endif
+      PROF_FLUSH(8, warp == kEpiWarps);
+      // no bulk copy may still be in flight when the block exits (matters after an abort)
+      if (loader)
+        for (uint32_t j = (it > (uint32_t)kStages ? it - kStages : 0u); j < it; ++j) mbar_wait_quiet(&S.full[j % kStages], (j / kStages) & 1);
+    } else if (warp == kMmaWarp) {
       // ========================================================================= MMA warp
-      constexpr uint32_t nm = ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      constexpr uint32_t nm = ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
       constexpr uint32_t idesc_i8 = (2u << 4) | (1u << 7) | (1u << 10) | nm;    // s32 accumulate, signed 8-bit operands
       constexpr uint32_t idesc_f8 = (1u << 4) | nm;                              // f32 accumulate, e4m3 operands
       constexpr uint32_t idesc_f16 = (1u << 4) | nm;                             // f32 accumulate, fp16 operands
       constexpr uint32_t idesc_f4 = (1u << 7) | (1u << 10) | (1u << 23) | nm;    // e2m1 operands, ue8m0 scales, K = 64
       uint32_t it = 0, ia = 0;
+      PROF_DECL;
+#ifdef DMOQ_IMG_PROFILE
+      const long long prof_start = clock64();
+#endif
       for (int item = 0; item < n_items; ++item) {
         for (int st = 0; st < steps_per_item; ++st, ++it) {
           const int s = it % kStages;
+          PROF_BEGIN();
           bool ok = mbar_wait(&S.full[s], (it / kStages) & 1, abort_flag);
+          PROF_END(0);
+          PROF_BEGIN();
           const int n_groups = (SPG == 2) ? 1 : min(GPS, G - st * GPS);
           // a group's first MMA needs its accumulator buffer back from the epilogue
           if (SPG == 1 || (st & 1) == 0) {
@@ -556,6 +628,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_img_kernel(const __grid_cons
               ok = mbar_wait(&S.acc_empty[ib % ACC], ((ib / ACC) & 1) ^ 1, abort_flag) && ok;
             }
           }
+          PROF_END(1);
+          PROF_BEGIN();
           tc_fence_after();
           if (lane == 0 && ok) {
             const uint64_t da = make_desc(smem_u32(&S.a[s][0]));
@@ -567,14 +641,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_img_kernel(const __grid_cons
 #pragma unroll
                 for (int k = 0; k < 2; ++k) {   // 64 elements = 32 bytes of K per instruction; scale bytes 2k, 2k+1
                   const uint32_t idesc = idesc_f4 | ((uint32_t)(2 * k) << 4) | ((uint32_t)(2 * k) << 29);
-                  tc_mma_mxf4(tmem_base + b * kBN, da + 2 * (2 * j + k), db + 2 * (2 * j + k), idesc, sfa, tmem_base + kSfbCol, k > 0);
+                  tc_mma_mxf4(tmem_base + b * BN, da + 2 * (2 * j + k), db + 2 * (2 * j + k), idesc, sfa, tmem_base + kSfbCol, k > 0);
                 }
                 tc_commit(&S.acc_full[b]);
               }
               tc_commit(&S.empty[s]);
             } else {
               const uint32_t b = ia % ACC;
-              const uint32_t d = tmem_base + b * kBN;
+              const uint32_t d = tmem_base + b * BN;
 #pragma unroll
               for (int k = 0; k < 4; ++k) {  // 32 bytes of K per instruction: +2 in 16-byte units
                 if (MODE == DMOQ_A8) tc_mma<DMOQ_A8>(d, da + 2 * k, db + 2 * k, idesc_i8, 1);  // the buffer holds the bias
@@ -587,8 +661,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_img_kernel(const __grid_cons
           }
           if (SPG == 1 || (st & 1)) ia += n_groups;
           __syncwarp();
+          PROF_END(2);
         }
       }
+#ifdef DMOQ_IMG_PROFILE
+      prof_acc[7] = clock64() - prof_start;
+#endif
+      PROF_FLUSH(16, true);
     }
   }
 
@@ -618,13 +697,14 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// Tensor map over a weight image seen as bytes: `rows` rows of `row_bytes`, copied in boxes of 128 bytes x 128 rows.
-int make_image_map(CUtensorMap* map, const void* image, size_t rows, size_t row_bytes) {
+// Tensor map over a byte matrix (a weight image, or the sorted activation-code table): `rows` rows of `row_bytes`
+// (a multiple of 16), copied in boxes of 128 bytes x box_rows rows (<= 256); rows past the end read as zero.
+int make_image_map(CUtensorMap* map, const void* image, size_t rows, size_t row_bytes, int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return DMOQ_EDEVICE;
   const cuuint64_t dims[2] = {row_bytes, rows};
   const cuuint64_t strides[1] = {row_bytes};
-  const cuuint32_t box[2] = {128, 128};
+  const cuuint32_t box[2] = {128, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(image), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -632,33 +712,33 @@ int make_image_map(CUtensorMap* map, const void* image, size_t rows, size_t row_
   return rc == CUDA_SUCCESS ? DMOQ_OK : DMOQ_EINVAL;
 }
 
-template <int MODE, int EPI>
-int launch(const CUtensorMap& map, const ImgArgs& a, int work_cap, cudaStream_t s) {
+template <int MODE, int EPI, int BN>
+int launch(const CUtensorMap& map_a, const CUtensorMap& map, const ImgArgs& a, int work_cap, cudaStream_t s) {
   static DmoqOncePerDevice once;
   bool* configured = once.slot();
   if (configured == nullptr) return DMOQ_EDEVICE;
-  const int bytes = (int)sizeof(Smem) + 1024;
+  const int bytes = (int)sizeof(Smem<BN>) + 1024;
   if (!*configured) {
     cudaFuncAttributes fa;
-    if (cudaFuncGetAttributes(&fa, gemm_img_kernel<MODE, EPI>) != cudaSuccess) return DMOQ_ELAUNCH;
-    if (fa.numRegs != kRegsLaunch) return DMOQ_ELAUNCH;   // the role budgets were sized for this pool
-    if (cudaFuncSetAttribute(gemm_img_kernel<MODE, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+    if (cudaFuncGetAttributes(&fa, gemm_img_kernel<MODE, EPI, BN>) != cudaSuccess) return DMOQ_ELAUNCH;
+    if (fa.numRegs != Cfg<BN>::kRegsLaunch) return DMOQ_ELAUNCH;   // the role budgets were sized for this pool
+    if (cudaFuncSetAttribute(gemm_img_kernel<MODE, EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
       return DMOQ_ELAUNCH;
     *configured = true;
   }
   int grid = dmoq_sm_count();
   if (grid > work_cap) grid = work_cap;
   if (grid < 1) grid = 1;
-  gemm_img_kernel<MODE, EPI><<<grid, kThreads, bytes, s>>>(map, a);
+  gemm_img_kernel<MODE, EPI, BN><<<grid, Cfg<BN>::kThreads, bytes, s>>>(map_a, map, a);
   return dmoq_launch_status();
 }
 
-template <int MODE>
-int launch_epi(const CUtensorMap& map, const ImgArgs& a, int epi, int work_cap, cudaStream_t s) {
+template <int MODE, int BN>
+int launch_epi(const CUtensorMap& map_a, const CUtensorMap& map, const ImgArgs& a, int epi, int work_cap, cudaStream_t s) {
   switch (epi) {
-    case DMOQ_EPI_SILU: return launch<MODE, DMOQ_EPI_SILU>(map, a, work_cap, s);
-    case DMOQ_EPI_WEIGHTED: return launch<MODE, DMOQ_EPI_WEIGHTED>(map, a, work_cap, s);
-    case DMOQ_EPI_PLAIN: return launch<MODE, DMOQ_EPI_PLAIN>(map, a, work_cap, s);
+    case DMOQ_EPI_SILU: return launch<MODE, DMOQ_EPI_SILU, BN>(map_a, map, a, work_cap, s);
+    case DMOQ_EPI_WEIGHTED: return launch<MODE, DMOQ_EPI_WEIGHTED, BN>(map_a, map, a, work_cap, s);
+    case DMOQ_EPI_PLAIN: return launch<MODE, DMOQ_EPI_PLAIN, BN>(map_a, map, a, work_cap, s);
     default: return DMOQ_EINVAL;
   }
 }
@@ -672,7 +752,7 @@ bool dmoq_img_supported(const dmoq_pool_t& p, int is_down, int hidden) {
   if (img == nullptr || nimg == nullptr) return false;
   if (p.inter % 128 != 0 || hidden % 128 != 0) return false;
   if (p.mode == DMOQ_FP4 && (p.inter / 128) % 2 != 0 && is_down && p.n_members > 1) return false;   // image groups pair up
-  return true;
+  return true;   // the caller also needs the code table in routed-row order (route->a_row == NULL, or the down side)
 }
 
 int dmoq_grouped_gemm_img(const dmoq_route_t* route, const dmoq_pool_t& p, int pool_index, int is_down, int epilogue,
@@ -681,7 +761,6 @@ int dmoq_grouped_gemm_img(const dmoq_route_t* route, const dmoq_pool_t& p, int p
   ImgArgs a{};
   a.tiles = reinterpret_cast<const DmoqTile*>(route->tiles);
   a.n_tiles = route->n_tiles;
-  a.a_row = is_down ? nullptr : route->a_row;
   a.row_weight = route->sorted_weights;
   a.pool = pool_index;
   a.is_down = is_down;
@@ -689,7 +768,6 @@ int dmoq_grouped_gemm_img(const dmoq_route_t* route, const dmoq_pool_t& p, int p
   a.hidden = hidden;
   a.norm_img = is_down ? p.dn_norm_img : p.gu_norm_img;
   a.n_img = is_down ? hidden : p.n_members * 2 * p.inter;
-  a.a_codes = static_cast<const uint8_t*>(a_codes);
   a.a_scales = static_cast<const uint8_t*>(a_scales);
   a.a_stride = a_stride;
   a.out = out;
@@ -707,20 +785,39 @@ int dmoq_grouped_gemm_img(const dmoq_route_t* route, const dmoq_pool_t& p, int p
     rows = (size_t)groups * a.n_img;
     row_bytes = (p.mode == DMOQ_A16) ? 256 : 128;
   }
-  CUtensorMap map;
-  const int rc = make_image_map(&map, is_down ? p.dn_img : p.gu_img, rows, row_bytes);
+  // 256-column tiles wherever the shape allows (not FP4: its scale-factor columns share TMEM with the accumulators)
+  const bool wide = p.mode != DMOQ_FP4 && partials == nullptr && (is_down ? hidden % 256 == 0 : p.inter % 128 == 0);
+  const int bn = wide ? 256 : 128;
+  CUtensorMap map, map_a;
+  int rc = make_image_map(&map, is_down ? p.dn_img : p.gu_img, rows, row_bytes, bn);
   if (rc != DMOQ_OK) return rc;
-  const int nb = is_down ? hidden / kBN : p.inter / (kBN / 2);
+  // the activation-code table: one row per routed row, in routed-row order
+  const size_t a_rows = (size_t)route->T * route->top_k + (route->has_shared ? (size_t)route->T : 0);
+  const size_t a_pitch = (p.mode == DMOQ_A16) ? (size_t)a_stride * 2 : (p.mode == DMOQ_FP4) ? (size_t)a_stride / 2 : (size_t)a_stride;
+  rc = make_image_map(&map_a, a_codes, a_rows, a_pitch, 128);
+  if (rc != DMOQ_OK) return rc;
+  const int nb = is_down ? hidden / bn : p.inter / (bn / 2);
   long long cap = (long long)route->tile_cap * nb;
   const int work_cap = cap > (1 << 30) ? (1 << 30) : (int)cap;
   switch (p.mode) {
-    case DMOQ_A16: return launch_epi<DMOQ_A16>(map, a, epilogue, work_cap, s);
-    case DMOQ_A8: return launch_epi<DMOQ_A8>(map, a, epilogue, work_cap, s);
-    case DMOQ_FP8: return launch_epi<DMOQ_FP8>(map, a, epilogue, work_cap, s);
-    case DMOQ_FP4: return launch_epi<DMOQ_FP4>(map, a, epilogue, work_cap, s);
+    case DMOQ_A16: return wide ? launch_epi<DMOQ_A16, 256>(map_a, map, a, epilogue, work_cap, s) : launch_epi<DMOQ_A16, 128>(map_a, map, a, epilogue, work_cap, s);
+    case DMOQ_A8: return wide ? launch_epi<DMOQ_A8, 256>(map_a, map, a, epilogue, work_cap, s) : launch_epi<DMOQ_A8, 128>(map_a, map, a, epilogue, work_cap, s);
+    case DMOQ_FP8: return wide ? launch_epi<DMOQ_FP8, 256>(map_a, map, a, epilogue, work_cap, s) : launch_epi<DMOQ_FP8, 128>(map_a, map, a, epilogue, work_cap, s);
+    case DMOQ_FP4: return launch_epi<DMOQ_FP4, 128>(map_a, map, a, epilogue, work_cap, s);
     default: return DMOQ_EINVAL;
   }
 }
+
+#ifdef DMOQ_IMG_PROFILE
+extern "C" int dmoq_img_profile(unsigned long long* out32, int reset) {
+  if (cudaMemcpyFromSymbol(out32, g_img_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return DMOQ_EDEVICE;
+  if (reset) {
+    unsigned long long z[32] = {0};
+    if (cudaMemcpyToSymbol(g_img_prof, z, sizeof(z)) != cudaSuccess) return DMOQ_EDEVICE;
+  }
+  return DMOQ_OK;
+}
+#endif
 
 // Status word of this file's kernels on the current device (0 = no bounded wait ever ran out); synchronises.
 int dmoq_img_status(int* out) {

@@ -570,8 +570,9 @@ extern "C" int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* p
 
   DMOQ_CHECK_ARG((is_down ? p.dn_idx : p.gu_idx) && (is_down ? p.dn_norm : p.gu_norm));
   DMOQ_CHECK_ARG(a_stride >= (is_down ? p.inter : hidden) && a_stride % kG == 0);
-  // a pool that comes with a weight image runs on the image-fed tensor-core kernel
-  if (route->tile_m == 128 && use_tc_path() && dmoq_img_supported(p, is_down, hidden))
+  // a pool that comes with a weight image runs on the image-fed tensor-core kernel, which takes whole tiles of the
+  // activation-code table: the table must be in routed-row order
+  if (route->tile_m == 128 && use_tc_path() && (is_down || route->a_row == nullptr) && dmoq_img_supported(p, is_down, hidden))
     return dmoq_grouped_gemm_img(route, p, pool_index, is_down, epilogue, hidden, a_codes, a_scales, a_stride, out,
                                  out_stride, partials, static_cast<cudaStream_t>(stream));
   if (route->tile_m == 128 && use_tc_path() && dmoq_tc_supported(p, is_down, hidden))

@@ -174,7 +174,6 @@ class _HostRoute:
         self.n_tiles = torch.tensor([len(tiles)] + [0] * (2 * MAX_POOLS - 1), **i32)
         self.rank = torch.tensor(list(ranks) if len(ranks) else [0], **i32)
         self.pool_of = torch.zeros(max(len(ranks), 1), **i32)
-        self.a_row = torch.arange(max(n_rows, 1), **i32)
         self.weights = (weights.to(torch.float32).contiguous() if weights is not None
                         else torch.ones(max(n_rows, 1), dtype=torch.float32, device=device))
         self.zeros = torch.zeros(MAX_POOLS, **i32)
@@ -182,7 +181,7 @@ class _HostRoute:
         r.T, r.top_k, r.E, r.has_shared = n_rows, 1, max(len(ranks), 1), 0
         r.tile_m, r.n_pools = TILE_M, 1
         r.expert_pool, r.expert_rank = self.pool_of.data_ptr(), self.rank.data_ptr()
-        r.sorted_weights, r.a_row = self.weights.data_ptr(), self.a_row.data_ptr()
+        r.sorted_weights = self.weights.data_ptr()   # a_row stays NULL: the callers' rows are already in routed-row order
         r.tiles, r.n_tiles, r.tile_cap = self.tiles.data_ptr(), self.n_tiles.data_ptr(), max(len(tiles), 1)
         r.pool_hoisted = self.zeros.data_ptr()
         self.c = r

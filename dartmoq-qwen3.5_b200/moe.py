@@ -19,6 +19,7 @@ import ctypes as C
 import math
 import os
 import time
+import weakref
 from typing import Dict, List, Optional
 
 import torch
@@ -29,6 +30,16 @@ from . import format as fmt
 from ._lib import A16, A8, FP8, FP4, EPI_PLAIN, EPI_SILU, EPI_WEIGHTED, MAX_POOLS, TILE_M, Pool, Route, check, ptr
 
 GROUP = fmt.GROUP_SIZE
+# Device memory this process may spend on resident weight images of the fp16 / INT8 / e4m3 modes (all layers
+# together; a 2-bit pool's INT8 image is four times its packed size).  Layers built after it runs out expand
+# transient images per forward instead.
+IMAGE_BUDGET = {"bytes_left": int(os.environ.get("DMOQ_IMAGE_BUDGET_GB", "96")) << 30}
+
+
+def _return_image_budget(n: int) -> None:
+    IMAGE_BUDGET["bytes_left"] += n
+
+
 _META_KEYS = ("seed", "group_size", "shape", "bit_width", "rotation", "orig_dtype")
 
 
@@ -362,18 +373,35 @@ class _Engine:
             return p.mode == FP8 and p.bit != 8
         self._ws: Dict[int, _Workspace] = {}
         self.last_launches = 0
-        # weight images: WxFP4 pools fold their codebooks into e2m1 images at load time (as the reference does, within
-        # its byte budget); the other modes expand a pool into a transient image per forward once an expert expects
-        # enough rows to repay the expansion ("auto"), always ("always", images then stay resident) or never
+        # Weight images (dmoq_expand_weights): a pool's codewords looked up once and kept in operand-row layout, so the
+        # tensor-core GEMM streams them with TMA copies.  WxFP4 pools need theirs (the reference folds codebooks into
+        # e2m1 at load time too, within its byte budget); the other modes trade memory for speed the same way:
+        #   "auto"       resident images while the process-wide budget lasts, else a transient image per forward once
+        #                an expert expects enough rows to repay the expansion
+        #   "transient"  never resident (FP4 excepted): packed weights stay the only copy
+        #   "always"     resident regardless of the budget;   "never": index expansion inside the GEMM only
         self.weight_images = getattr(m, "weight_images", "auto")
         self.image_min_rows = int(getattr(m, "weight_image_min_rows", 192))
-        budget = int(getattr(m, "_FOLD_BYTES_BUDGET", 16 << 30))
+        fold_budget = int(getattr(m, "_FOLD_BYTES_BUDGET", 16 << 30))
         self._img_scratch = None
         for p in self.pools:
-            want = self.weight_images != "never" and (p.mode == FP4 or self.weight_images == "always")
-            if want and sum(p.img_bytes) > 0 and sum(p.img_bytes) <= budget:
+            need = sum(p.img_bytes)
+            if need == 0 or self.weight_images == "never":
+                continue
+            if p.mode == FP4:
+                ok = need <= fold_budget
+                fold_budget -= need if ok else 0
+            elif self.weight_images == "always":
+                ok = True
+            elif self.weight_images == "auto":
+                ok = need <= IMAGE_BUDGET["bytes_left"]
+                if ok:
+                    IMAGE_BUDGET["bytes_left"] -= need
+                    weakref.finalize(self, _return_image_budget, need)   # handed back when this engine goes away
+            else:
+                ok = False
+            if ok:
                 p.build_resident_images()
-                budget -= sum(p.img_bytes)
         self.all_tensor_core = all(_tc(p) or p.img[0] is not None or p.n_members < 8 for p in self.pools)
 
     def _image_scratch(self) -> torch.Tensor:
@@ -460,8 +488,27 @@ class _Engine:
         r.tiles, r.n_tiles, r.tile_cap = ws.tiles.data_ptr(), ws.n_tiles.data_ptr(), ws.tile_cap
         r.pool_hoisted = self.pool_hoisted.data_ptr()
         ws.route = r
+        # the same tables for GEMMs that read an activation-code table already in routed-row order (a_row = NULL)
+        rs = Route.from_buffer_copy(r)
+        rs.a_row = None
+        ws.route_sorted = rs
+        ws.sorted_codes = ws.sorted_scales = None
         self._ws[T] = ws
         return ws
+
+    def _sorted_tables(self, ws: "_Workspace"):
+        """Gate_up-side activation codes and scales in routed-row order, shared by the pools of one forward (each
+        pool's rows are gathered right before its GEMM).  Row pitch: ``sorted_stride`` elements, a multiple of 512
+        so that a row's fp16 scales sit on 8-byte boundaries."""
+        if ws.sorted_codes is None:
+            stride = (self.hidden + 511) // 512 * 512
+            ws.sorted_stride = stride
+            rows = max(ws.R, 1)
+            ws.sorted_codes = torch.empty(rows * max(p.code_bytes(stride) for p in self.pools), dtype=torch.uint8,
+                                          device=self.device)
+            ws.sorted_scales = torch.empty(max(rows * max(p.scale_bytes(stride) for p in self.pools), 16),
+                                           dtype=torch.uint8, device=self.device)
+        return ws.sorted_codes, ws.sorted_scales, ws.sorted_stride
 
     # ------------------------------------------------------------------ one forward
     def run(self, x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor,
@@ -517,9 +564,24 @@ class _Engine:
                 mark("expand_gate_up:" + p.key)
             self.pool_array[i] = p.c
             part = None if partials is None else partials.get(("gate_up", p.key))
-            check(lib.dmoq_grouped_gemm(C.byref(ws.route), self.pool_array, i, 0, EPI_SILU, self.hidden,
-                                        ptr(ws.act_codes[i]), ptr(ws.act_scales[i]), self.hidden,
-                                        ptr(ws.act), self.inter_max, ptr(part), s), "dmoq_grouped_gemm(gate_up)")
+            if img:
+                # the image-fed kernel takes whole tiles of the code table: this pool's rows go into routed-row order
+                codes, scales, stride = self._sorted_tables(ws)
+                has_scales = p.scale_bytes(self.hidden) > 0
+                check(lib.dmoq_gather_rows(C.byref(ws.route), i, ptr(ws.act_codes[i]), p.code_bytes(self.hidden),
+                                           p.code_bytes(self.hidden), ptr(codes), p.code_bytes(stride),
+                                           ptr(ws.act_scales[i]) if has_scales else None, p.scale_bytes(self.hidden),
+                                           p.scale_bytes(self.hidden), ptr(scales) if has_scales else None,
+                                           p.scale_bytes(stride), s), "dmoq_gather_rows")
+                self.last_launches += 1
+                mark("gather:" + p.key)
+                check(lib.dmoq_grouped_gemm(C.byref(ws.route_sorted), self.pool_array, i, 0, EPI_SILU, self.hidden,
+                                            ptr(codes), ptr(scales), stride,
+                                            ptr(ws.act), self.inter_max, ptr(part), s), "dmoq_grouped_gemm(gate_up)")
+            else:
+                check(lib.dmoq_grouped_gemm(C.byref(ws.route), self.pool_array, i, 0, EPI_SILU, self.hidden,
+                                            ptr(ws.act_codes[i]), ptr(ws.act_scales[i]), self.hidden,
+                                            ptr(ws.act), self.inter_max, ptr(part), s), "dmoq_grouped_gemm(gate_up)")
             mark("gate_up_silu:" + p.key)
             check(lib.dmoq_rotate_quant_down(C.byref(ws.route), self.pool_array, i, ptr(ws.act), self.inter_max,
                                              ptr(ws.dn_codes), ptr(ws.dn_scales), self.inter_max, s),

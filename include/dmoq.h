@@ -112,7 +112,8 @@ typedef struct dmoq_route {
   int32_t* sorted_tokens;     /* (R) token of each row, R = T*top_k + has_shared*T             */
   float* sorted_weights;      /* (R) routing weight of each row                                */
   int32_t* row_of;            /* (R) row of flat (token, slot) pair; shared rows follow        */
-  int32_t* a_row;             /* (R) row of the pool's activation-code table feeding this row  */
+  int32_t* a_row;             /* (R) row of the pool's activation-code table feeding this row;
+                                 the GEMMs accept NULL = the table is in routed-row order      */
   int32_t* pool_rows;         /* (DMOQ_MAX_POOLS) rows routed to each pool                     */
   int32_t* pool_src;          /* for non-hoisted pools: token of each compact table row,
                                  pool p's list starts at pool_src_base[p]; size = sum of the
@@ -272,6 +273,18 @@ int dmoq_widen_indices(const uint8_t* packed, int64_t n_bytes, int32_t bit, uint
  * G = hidden/128 (gate_up) or n_members*inter/128 (down).  dmoq_weight_image_bytes gives the image size;
  * the norm image holds G*N floats.  Reads pool->{gu,dn}_{idx,norm,lut}, bit, mode, identity_lut, n_members, inter.
  */
+/*
+ * Rows of a pool's activation-code table put into routed-row order: for every row r of the pool's tiles,
+ * dst row r = src row route->a_row[r] (row_bytes of codes, scale_bytes of scales; the scale pointers may both be
+ * NULL).  After it the pool's GEMM can take whole 128-row tiles of the table with tensor-map copies; it then gets a
+ * route whose a_row is NULL (= a row reads the table row of its own index).  Replaces the gather
+ * x_pool = hoisted[pool_tokens] of quantization/wxa16/bit_partitioned_moe.py:893-900.
+ */
+int dmoq_gather_rows(const dmoq_route_t* route, int32_t pool_index, const void* src_codes, int32_t src_pitch_bytes,
+                     int32_t row_bytes, void* dst_codes, int32_t dst_pitch_bytes, const void* src_scales,
+                     int32_t src_scale_pitch, int32_t scale_bytes, void* dst_scales, int32_t dst_scale_pitch,
+                     void* stream);
+
 size_t dmoq_weight_image_bytes(const dmoq_pool_t* pool, int32_t is_down, int32_t hidden);
 int dmoq_expand_weights(const dmoq_pool_t* pool, int32_t is_down, int32_t hidden, void* image, float* norm_image,
                         void* stream);

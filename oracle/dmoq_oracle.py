@@ -555,18 +555,30 @@ def dequant_matmul_forward(layer: Layer, x: torch.Tensor, topk_w: np.ndarray, to
                            shared_w: Optional[np.ndarray] = None, dtype=torch.float32,
                            weight_cache: Optional[dict] = None) -> np.ndarray:
     """The reference's dequantize-then-matmul path (turboquant_utils/test_triton_mp_moe_e2e_bench.py:167-272):
-    per expert, dequantise its gate_up rows / down columns, x @ W^T, silu*up, @ W_down^T, weight, scatter-add.
+    per ACTIVE expert, dequantise its gate_up rows / down columns, x @ W^T, silu*up, @ W_down^T, weight, scatter-add.
     ``dtype`` float16 reproduces the reference's arithmetic type; float32 is the "ideal" answer."""
     T, H = x.shape
     xt = x.detach().cpu().to(dtype)
     tokens, weights, starts, _ = sort_rows(np.asarray(topk_idx), np.asarray(topk_w, np.float32), layer.n_experts)
     y = torch.zeros(T, H, dtype=dtype)
 
-    def dense(p, side):
-        key = (id(p), side)
+    def expert_weights(p, rank):
+        """(gate_up rows, down columns) of one member, dequantised on their own as the reference does per expert and
+        bit (turboquant_dequantize_packed_rows / _cols, test_triton_mp_moe_e2e_bench.py:214-238)."""
+        key = (id(p), rank)
         if weight_cache is not None and key in weight_cache:
             return weight_cache[key]
-        w = torch.from_numpy(dequantize_packed(p[side])).to(torch.float16).to(dtype)
+        inter, bit = p["inter"], p["bit"]
+        gu, dn = p["gu"], p["dn"]
+        r0, r1 = 2 * inter * rank, 2 * inter * (rank + 1)
+        rows = dict(gu, indices_packed=np.asarray(gu["indices_packed"])[r0:r1], norms=np.asarray(gu["norms"])[r0:r1],
+                    shape=(r1 - r0, gu["shape"][1]))
+        c0, c1 = inter * rank, inter * (rank + 1)
+        cols = dict(dn, indices_packed=np.asarray(dn["indices_packed"])[:, c0 * bit // 8:c1 * bit // 8],
+                    norms=np.asarray(dn["norms"])[:, c0 // GS:c1 // GS], shape=(dn["shape"][0], inter),
+                    seed=int(dn["seed"]) + c0)
+        w = (torch.from_numpy(dequantize_packed(rows)).to(torch.float16).to(dtype),
+             torch.from_numpy(dequantize_packed(cols)).to(torch.float16).to(dtype))
         if weight_cache is not None:
             weight_cache[key] = w
         return w
@@ -574,17 +586,17 @@ def dequant_matmul_forward(layer: Layer, x: torch.Tensor, topk_w: np.ndarray, to
     pools = list(layer.pools) + ([layer.shared] if layer.shared is not None else [])
     for p in pools:
         inter = p["inter"]
-        w_gu, w_dn = dense(p, "gu"), dense(p, "dn")
         if p is layer.shared:
             members = [(0, np.arange(T), np.ones(T, np.float32) if shared_w is None else np.asarray(shared_w, np.float32))]
         else:
             members = [(rank, tokens[starts[e]:starts[e + 1]], weights[starts[e]:starts[e + 1]])
                        for rank, e in enumerate(p["members"]) if starts[e + 1] > starts[e]]
         for rank, tok, w in members:
+            w_gu, w_dn = expert_weights(p, rank)
             xe = xt[torch.from_numpy(tok.astype(np.int64))]
-            gu = xe @ w_gu[2 * inter * rank:2 * inter * (rank + 1)].T
+            gu = xe @ w_gu.T
             act = torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]
-            out = act @ w_dn[:, inter * rank:inter * (rank + 1)].T
+            out = act @ w_dn.T
             out = out * torch.from_numpy(np.asarray(w, np.float32)).to(dtype).unsqueeze(1)
             y.index_add_(0, torch.from_numpy(tok.astype(np.int64)), out)
     return y.float().numpy()
