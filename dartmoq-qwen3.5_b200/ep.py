@@ -169,7 +169,7 @@ class ExpertParallelMoE(torch.nn.Module):
     """
 
     def __init__(self, gate, local_moe, num_experts: int, top_k: int, shared_expert=None,
-                 shared_expert_gate=None, group=None, exchange: str = "rows"):
+                 shared_expert_gate=None, group=None, exchange: str = "rows", full_layer=None):
         super().__init__()
         if exchange not in ("rows", "gather"):
             raise ValueError(f"exchange must be 'rows' or 'gather', got {exchange!r}")

@@ -411,6 +411,20 @@ class _Engine:
             self._img_scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=self.device)
         return self._img_scratch
 
+    def prepare(self, T: int) -> "_Workspace":
+        """Everything a forward of ``T`` tokens allocates or copies from the host, done now: the workspace, the
+        routed-order code tables, norm images and the transient image buffer.  A stream capture must find all of it
+        in place (allocations and host copies are not capturable)."""
+        ws = self.workspace(T)
+        for p in self.pools:
+            mode = self._image_mode(p, T, ws.tile_m)
+            if mode:
+                p.build_norm_images()
+                self._sorted_tables(ws)
+            if mode == 2:
+                self._image_scratch()
+        return ws
+
     def _image_mode(self, p: "_PoolRuntime", T: int, tile_m: int) -> int:
         """0: no image (index expansion inside the GEMM), 1: resident image, 2: transient image this forward."""
         if tile_m != TILE_M or self.weight_images == "never":
@@ -819,6 +833,7 @@ class WxA16BitPartitionedGroupMoE(nn.Module):
             if len(self._graphs) > 8:
                 self._graphs = {key: "warm"}
             static_x = x.clone()
+            eng.prepare(x.shape[0])          # nothing may be allocated or copied from the host inside the capture
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
