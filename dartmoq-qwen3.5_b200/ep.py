@@ -171,8 +171,11 @@ class ExpertParallelMoE(torch.nn.Module):
     def __init__(self, gate, local_moe, num_experts: int, top_k: int, shared_expert=None,
                  shared_expert_gate=None, group=None, exchange: str = "rows", full_layer=None):
         super().__init__()
-        if exchange not in ("rows", "gather"):
-            raise ValueError(f"exchange must be 'rows' or 'gather', got {exchange!r}")
+        if exchange not in ("rows", "gather", "codes"):
+            raise ValueError(f"exchange must be 'rows', 'gather' or 'codes', got {exchange!r}")
+        if exchange == "codes" and full_layer is None:
+            raise ValueError("exchange='codes' needs full_layer: the unsharded module (its codebooks, seeds and expert "
+                             "offsets; the weights themselves are not used)")
         want_k = top_k if exchange == "gather" else 1
         if local_moe.top_k != want_k:
             raise ValueError(f"exchange={exchange!r} needs a local module with top_k={want_k} "
@@ -187,6 +190,11 @@ class ExpertParallelMoE(torch.nn.Module):
         self.group, self.exchange = group, exchange
         self._shared_layer: list = []         # [module or None] once resolved; a list keeps it out of the submodules
         self._side_stream: list = []
+        self._codes: list = []                # the code exchange's state, built on the first forward
+        self._full_meta = [full_layer] if exchange == "codes" else []
+        self.profile = False                  # codes exchange: per-stage device times into last_stage_ms
+        self.last_stage_ms = None
+        self.last_launches = 0
 
     def _local_partial(self, x_all, w_all, local_idx):
         eng = self.local_moe._get_engine(x_all.device)
@@ -247,6 +255,26 @@ class ExpertParallelMoE(torch.nn.Module):
             y = ep_forward_gathered(x, w, idx, self.num_experts // world, self._local_partial, self.group,
                                     extra=joined if shared is not None else None)
             main.wait_stream(side)
+        elif self.exchange == "codes":
+            if not x.is_cuda:
+                raise RuntimeError("the code exchange runs on CUDA devices only")
+            if not self._codes:
+                from .ep_codes import CodesExchange
+                self._codes.append(CodesExchange(self._full_meta.pop(), self.local_moe, self.num_experts, self.top_k,
+                                                 self.group, x.device))
+            main = torch.cuda.current_stream()
+            if not self._side_stream:
+                self._side_stream.append(torch.cuda.Stream(device=x.device))
+            side = self._side_stream[0]
+            side.wait_stream(main)
+            with torch.cuda.stream(side):       # the token-local shared expert, beside the exchanges
+                shared = self._shared_partial(x)
+            cx = self._codes[0]
+            y = cx.forward(x, w, idx, profile=self.profile)
+            main.wait_stream(side)
+            if shared is not None:
+                y = (y.float() + shared.float()).to(y.dtype)
+            self.last_stage_ms, self.last_launches = cx.last_stage_ms, cx.last_launches
         elif self.exchange == "gather":
             shared = None
             y = ep_forward_gathered(x, w, idx, self.num_experts // world, self._local_partial, self.group)

@@ -94,3 +94,31 @@ def test_shard_experts_slices_the_packed_pools():
                 assert p._offsets_lists()[bs][-1] == offs[bs][4 * i + 4] - offs[bs][4 * i]
     assert type(parts[0]) is type(moe) and parts[0].top_k == 1 and parts[0].num_experts == 4
     assert ep.shard_experts(moe, 0, 4, top_k=2).top_k == 2
+
+
+def test_owner_tile_plan_covers_every_received_row_once():
+    """The owner's tile lists, built from the (source, expert) count matrix: every received row is covered exactly
+    once, by a tile of its own expert in that expert's pool, inside one (source, expert) segment."""
+    sys.path.insert(0, ROOT)
+    from dartmoq_b200.ep_codes import owner_tiles
+    rng = np.random.default_rng(3)
+    n_src, e_loc = 4, 9
+    counts = rng.integers(0, 400, size=(n_src, e_loc))
+    counts[1, :] = 0                       # a source with an empty batch
+    counts[:, 4] = 0                       # an expert nobody routed to
+    pool_of = np.array([0, 1, 0, 2, 0, 1, 1, 0, 2])
+    rank_of = np.array([0, 0, 1, 0, 2, 1, 2, 3, 1])
+    tiles, n_tiles = owner_tiles(counts, pool_of, rank_of, 3)
+    total = int(counts.sum())
+    cover = np.zeros(total, np.int32)
+    starts = np.concatenate([[0], np.cumsum(counts.reshape(-1))])
+    for p in range(3):
+        n, base = n_tiles[p], n_tiles[8 + p]
+        for e, row0, rows, rank in tiles[base:base + n]:
+            assert pool_of[e] == p and rank == rank_of[e] and 0 < rows <= 128
+            seg = np.searchsorted(starts, row0, side="right") - 1          # the (source, expert) segment of row0
+            assert seg % e_loc == e and row0 + rows <= starts[seg + 1]
+            cover[row0:row0 + rows] += 1
+    assert (cover == 1).all() and n_tiles[:3].sum() == tiles.shape[0]
+    empty, n0 = owner_tiles(np.zeros((2, 3), np.int64), np.array([0, 0, 1]), np.array([0, 1, 0]), 2)
+    assert empty.shape == (0, 4) and n0.sum() == 0
