@@ -190,8 +190,16 @@ class ExpertParallelMoE(torch.nn.Module):
         self.group, self.exchange = group, exchange
         self._shared_layer: list = []         # [module or None] once resolved; a list keeps it out of the submodules
         self._side_stream: list = []
-        self._codes: list = []                # the code exchange's state, built on the first forward
+        self._codes: list = []                # the code exchange's state
         self._full_meta = [full_layer] if exchange == "codes" else []
+        if exchange == "codes":
+            # built now where the device is known: only the unsharded layer's metadata (codebooks, seeds, expert
+            # offsets) is read, so the caller may drop that layer's weights right after
+            dev = next((b.device for b in local_moe.buffers()), None)
+            if dev is not None and dev.type == "cuda":
+                from .ep_codes import CodesExchange
+                with torch.cuda.device(dev):
+                    self._codes.append(CodesExchange(self._full_meta.pop(), local_moe, num_experts, top_k, group, dev))
         self.profile = False                  # codes exchange: per-stage device times into last_stage_ms
         self.last_stage_ms = None
         self.last_launches = 0
