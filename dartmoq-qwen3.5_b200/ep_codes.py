@@ -35,23 +35,26 @@ from ._lib import A16, EPI_PLAIN, EPI_SILU, MAX_POOLS, TILE_M, Route, check, ptr
 GROUP = fmt.GROUP_SIZE
 
 
-def owner_tiles(counts: np.ndarray, pool_of: np.ndarray, rank_of: np.ndarray, n_pools: int, tile_m: int = TILE_M):
+def owner_tiles(counts: np.ndarray, pool_of: np.ndarray, rank_of: np.ndarray, n_pools: int, tile_m: int = TILE_M,
+                expert0: int = 0, row_base: int = 0):
     """Tile lists over a receive buffer laid out source by source, each source's rows sorted by local expert.
 
     counts (N_src, E_local): rows source s sends for local expert e.  Returns (tiles (n, 4) int32 rows of
     (expert, first row, row count, member rank), pool p's tiles contiguous; n_tiles (2*MAX_POOLS,) = tiles per pool
-    then each pool's first tile).  A (source, expert) pair's rows are cut into tiles of at most ``tile_m`` rows."""
+    then each pool's first tile).  A (source, expert) pair's rows are cut into tiles of at most ``tile_m`` rows.
+    ``counts`` may be a column block of the full matrix: its first column is local expert ``expert0`` and its rows
+    start at ``row_base`` of the receive buffer."""
     n_src, e_loc = counts.shape
     flat = counts.reshape(-1).astype(np.int64)
-    seg_start = np.concatenate([[0], np.cumsum(flat)[:-1]])            # arrival order: source major, expert minor
-    seg_expert = np.tile(np.arange(e_loc), n_src)
+    seg_start = row_base + np.concatenate([[0], np.cumsum(flat)[:-1]])   # arrival order: source major, expert minor
+    seg_expert = expert0 + np.tile(np.arange(e_loc), n_src)
     seg_tiles = (flat + tile_m - 1) // tile_m
     tiles_out, n_tiles = [], np.zeros(2 * MAX_POOLS, np.int32)
     base = 0
     for p in range(n_pools):
         sel = np.nonzero((pool_of[seg_expert] == p) & (flat > 0))[0]
         # experts in index order, sources in rank order inside an expert (keeps one expert's weights hot in L2)
-        sel = sel[np.lexsort((sel // e_loc, seg_expert[sel]))]
+        sel = sel[np.lexsort((sel // e_loc, seg_expert[sel]))]   # sel // e_loc = source rank
         nt = seg_tiles[sel]
         total = int(nt.sum())
         if total:
@@ -120,6 +123,9 @@ class CodesExchange:
         self.stride = (self.H + 511) // 512 * 512                      # elements per row of the exchanged tables
         self._ws = {}
         self._pinned = None
+        self._comm_stream = None
+        self._pool_of = self._rank_of = None
+        self.n_chunks = 4               # blocks of each owner's experts the exchange is pipelined over
         self._owner_cap = 0
         self.last_stage_ms = None
         self.last_launches = 0
@@ -198,22 +204,25 @@ class CodesExchange:
             self.ones = torch.ones(cap, dtype=torch.float32, device=dev)
             self._owner_cap = cap
 
-    def _owner_compute(self, counts: np.ndarray, n_recv: int, s, mark):
-        """Grouped GEMMs of the local experts over the receive buffer as it arrived."""
-        lib = self.lib
+    def _owner_route(self, counts: np.ndarray, expert0: int, row_base: int, n_rows_total: int):
+        """Route struct + tile tensors for the rows of local experts [expert0, expert0 + counts.shape[1]) that start at
+        ``row_base`` of the receive buffer."""
         eng = self.local_moe._get_engine(self.device)
-        pool_of = eng.expert_pool.cpu().numpy()[:self.E_loc]
-        rank_of = eng.expert_rank.cpu().numpy()[:self.E_loc]
-        tiles_np, n_tiles_np = owner_tiles(counts, pool_of, rank_of, len(eng.pools))
-        i32 = dict(dtype=torch.int32, device=self.device)
+        tiles_np, n_tiles_np = owner_tiles(counts, self._pool_of, self._rank_of, len(eng.pools), TILE_M, expert0, row_base)
         tiles = torch.from_numpy(tiles_np if tiles_np.size else np.zeros((1, 4), np.int32)).to(self.device, non_blocking=True)
         n_tiles = torch.from_numpy(n_tiles_np).to(self.device, non_blocking=True)
         r = Route()
-        r.T, r.top_k, r.E, r.has_shared, r.tile_m, r.n_pools = n_recv, 1, self.E_loc, 0, TILE_M, len(eng.pools)
+        r.T, r.top_k, r.E, r.has_shared, r.tile_m, r.n_pools = n_rows_total, 1, self.E_loc, 0, TILE_M, len(eng.pools)
         r.expert_pool, r.expert_rank = eng.expert_pool.data_ptr(), eng.expert_rank.data_ptr()
         r.sorted_weights = self.ones.data_ptr()
         r.tiles, r.n_tiles, r.tile_cap = tiles.data_ptr(), n_tiles.data_ptr(), max(int(tiles_np.shape[0]), 1)
         r.pool_hoisted = self.pool_hoisted.data_ptr()
+        return r, n_tiles_np, (tiles, n_tiles)
+
+    def _owner_compute(self, r, n_tiles_np, s):
+        """Grouped GEMMs of the local experts over (a part of) the receive buffer as it arrived."""
+        lib = self.lib
+        eng = self.local_moe._get_engine(self.device)
         for i, p in enumerate(eng.pools):
             if n_tiles_np[i] == 0:
                 continue
@@ -233,16 +242,21 @@ class CodesExchange:
                                         ptr(self.dn_scales), eng.inter_max, ptr(self.dn), self.H, None, s),
                   "dmoq_grouped_gemm(down)")
             self.last_launches += 3
-        self._keep = (tiles, n_tiles)     # alive until the stream has consumed them
-        mark("owner_experts")
 
     # ------------------------------------------------------------------ one forward
     def forward(self, x: torch.Tensor, topk_w: torch.Tensor, topk_idx: torch.Tensor, profile: bool = False) -> torch.Tensor:
-        """x (T, H) local tokens -> routed experts' contribution (T, H), bit-identical to the unsharded layer's."""
+        """x (T, H) local tokens -> routed experts' contribution (T, H), bit-identical to the unsharded layer's.
+
+        The exchange is cut into ``n_chunks`` blocks of each owner's experts.  The collectives run on a second stream:
+        while the owner computes block c, block c+1's codes arrive and block c-1's results travel back."""
         lib, dev, N = self.lib, self.device, self.world
         T = x.shape[0]
         ws = self._workspace(T)
-        s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        main = torch.cuda.current_stream()
+        s = C.c_void_p(main.cuda_stream)
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=dev)
+        comm = self._comm_stream
         events, names = [], []
 
         def mark(name):
@@ -256,7 +270,7 @@ class CodesExchange:
         is_bf16 = int(x.dtype == torch.bfloat16)
         topk_idx = topk_idx.to(torch.int64).contiguous()
         topk_w = topk_w.to(torch.float32).contiguous()
-        # ---- token's rank: route, rotate + quantise once per bit pool, rows into routed order
+        # ---- token's rank: route, exchange the per-expert counts, rotate + quantise once per bit pool, rows into routed order
         check(lib.dmoq_route_build(C.byref(ws.route), ptr(topk_idx), ptr(topk_w), None, ptr(ws.route_ws),
                                    ws.route_ws.numel(), s), "dmoq_route_build")
         counts_dev = (ws.expert_rows[1:] - ws.expert_rows[:-1]).reshape(N, self.E_loc).contiguous()
@@ -281,25 +295,72 @@ class CodesExchange:
                                        p.scale_bytes(self.stride), s), "dmoq_gather_rows")
             self.last_launches += 2
         mark("route_rotate_gather")
-        # ---- exchange: split sizes (the one host synchronisation), then codes and scales
+        front_done = torch.cuda.Event()
+        front_done.record()
+        # ---- split sizes (the one host synchronisation)
         ev_counts.synchronize()
-        send_c, recv_c = both[0].numpy(), both[1].numpy()
-        send = send_c.sum(1).tolist()
-        recv = recv_c.sum(1).tolist()
-        n_recv = int(sum(recv))
+        send_c, recv_c = both[0].numpy().astype(np.int64), both[1].numpy().astype(np.int64)
+        n_recv = int(recv_c.sum())
         self._owner_buffers(n_recv)
-        dist.all_to_all_single(self.recv_codes[:n_recv], ws.send_codes[:ws.R], output_split_sizes=recv,
-                               input_split_sizes=send, group=self.group)
-        if self.mode != A16:
-            dist.all_to_all_single(self.recv_scales[:n_recv], ws.send_scales[:ws.R], output_split_sizes=recv,
-                                   input_split_sizes=send, group=self.group)
-        mark("dispatch_all_to_all")
-        # ---- owner: local experts over the rows as they arrived
-        self._owner_compute(recv_c, n_recv, s, mark)
-        # ---- back: fp16 rows in arrival order = the sender's routed order; then the single-GPU combine
-        dist.all_to_all_single(ws.back[:ws.R], self.dn[:n_recv], output_split_sizes=send, input_split_sizes=recv,
-                               group=self.group)
-        mark("combine_all_to_all")
+        eng = self.local_moe._get_engine(dev)
+        if self._pool_of is None:
+            self._pool_of = eng.expert_pool.cpu().numpy()[:self.E_loc]
+            self._rank_of = eng.expert_rank.cpu().numpy()[:self.E_loc]
+        n_chunks = max(1, min(self.n_chunks, self.E_loc))
+        edges = [self.E_loc * c // n_chunks for c in range(n_chunks + 1)]
+        send_start = np.concatenate([[0], np.cumsum(send_c.reshape(-1))])     # first routed row of every global expert
+        keep = []
+        recv_base = 0
+        comm.wait_event(front_done)
+        chunks = []
+        for c in range(n_chunks):
+            c0, c1 = edges[c], edges[c + 1]
+            sub_recv = recv_c[:, c0:c1]
+            rows_c = int(sub_recv.sum())
+            in_codes, in_scales, out_codes, out_scales, back_in, back_out = [], [], [], [], [], []
+            off = recv_base
+            for peer in range(N):
+                a0 = int(send_start[peer * self.E_loc + c0])
+                a1 = int(send_start[peer * self.E_loc + c1])
+                in_codes.append(ws.send_codes[a0:a1])
+                in_scales.append(ws.send_scales[a0:a1])
+                back_out.append(ws.back[a0:a1])
+                n_from = int(sub_recv[peer].sum())
+                out_codes.append(self.recv_codes[off:off + n_from])
+                out_scales.append(self.recv_scales[off:off + n_from])
+                back_in.append(self.dn[off:off + n_from])
+                off += n_from
+            chunks.append((c0, sub_recv, recv_base, rows_c, in_codes, in_scales, out_codes, out_scales, back_in, back_out))
+            recv_base += rows_c
+        arrived = []
+        with torch.cuda.stream(comm):
+            for ch in chunks:      # all dispatches are queued first: block c+1 travels while block c is computed
+                dist.all_to_all(ch[6], ch[4], group=self.group)
+                if self.mode != A16:
+                    dist.all_to_all(ch[7], ch[5], group=self.group)
+                ev = torch.cuda.Event()
+                ev.record(comm)
+                arrived.append(ev)
+        for c, ch in enumerate(chunks):
+            c0, sub_recv, base, rows_c = ch[0], ch[1], ch[2], ch[3]
+            main.wait_event(arrived[c])
+            if c == 0:
+                mark("first_block_arrived")
+            r, n_tiles_np, alive = self._owner_route(sub_recv, c0, base, n_recv)
+            keep.append(alive)
+            self._owner_compute(r, n_tiles_np, s)
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(comm):      # the block's fp16 rows go back in arrival order = the sender's routed order
+                comm.wait_event(done)
+                dist.all_to_all(ch[9], ch[8], group=self.group)
+        mark("owner_experts")
+        back_done = torch.cuda.Event()
+        back_done.record(comm)
+        main.wait_event(back_done)
+        mark("last_block_back")
+        self._keep = keep          # tile tensors stay alive until the stream has consumed them
+        # ---- token's rank: the single-GPU combine
         y = torch.empty_like(x)
         check(lib.dmoq_combine_weighted(C.byref(ws.route), ptr(ws.back), self.H, ptr(y), is_bf16, s), "dmoq_combine_weighted")
         self.last_launches += 2
