@@ -403,6 +403,10 @@ class _Engine:
             if ok:
                 p.build_resident_images()
         self.all_tensor_core = all(_tc(p) or p.img[0] is not None or p.n_members < 8 for p in self.pools)
+        # small batches of a WxA16 layer take the streaming decode kernels (packed indices, 32-row tiles, one launch for
+        # all pools): every pool fp16, 8-bit pools only with the computable uniform codebook
+        self.decode_ok = (bool(getattr(m, "enable_decode_kernels", True)) and self.hidden % 256 == 0
+                          and all(p.mode == A16 and (p.bit != 8 or p.identity) for p in self.pools))
 
     def _image_scratch(self) -> torch.Tensor:
         """One buffer for the transient image of whichever pool / projection is being computed."""
@@ -466,7 +470,8 @@ class _Engine:
         # are not padded to 128 rows; pools the tcgen05 kernel covers stay on 128-row tiles, it is the faster one
         # at every batch size (0.53 ms against 0.74 ms at 64 tokens on the 35B-A3B-like INT8 layer)
         small = T <= 256 and T * self.k_v <= 8 * self.E_v
-        ws.tile_m = 32 if (small and not self.all_tensor_core) else TILE_M
+        ws.decode = small and self.decode_ok
+        ws.tile_m = 32 if (small and (self.decode_ok or not self.all_tensor_core)) else TILE_M
         ws.tile_cap = (R + ws.tile_m - 1) // ws.tile_m + n_entries
         ws.tiles = torch.zeros(ws.tile_cap, 4, **i32)
         bases, total = [], 0
@@ -561,6 +566,25 @@ class _Engine:
                                         ws.caps[i], n_dev, p.c.gu_act_scale, ptr(ws.act_codes[i]),
                                         ptr(ws.act_scales[i]), s), "dmoq_rotate_quant")
         mark("rotate_quant")
+        if ws.decode:
+            # small batch: one streaming launch per projection for all pools
+            check(lib.dmoq_moe_decode_gateup(C.byref(ws.route), self.pool_array, len(self.pools), self.hidden,
+                                             ptr(ws.act), self.inter_max, s), "dmoq_moe_decode_gateup")
+            mark("decode_gate_up_silu")
+            for i, p in enumerate(self.pools):
+                check(lib.dmoq_rotate_quant_down(C.byref(ws.route), self.pool_array, i, ptr(ws.act), self.inter_max,
+                                                 ptr(ws.dn_codes), ptr(ws.dn_scales), self.inter_max, s),
+                      "dmoq_rotate_quant_down")
+            mark("rotate_quant_down")
+            check(lib.dmoq_moe_decode_down(C.byref(ws.route), self.pool_array, len(self.pools), self.hidden,
+                                           ptr(ws.dn_codes), self.inter_max, ptr(ws.dn), s), "dmoq_moe_decode_down")
+            mark("decode_down")
+            self.last_launches = (1 if T * self.k_v <= 1024 and T <= 4096 else 3) + 2 * len(self.pools) + 3
+            y = torch.empty_like(x)
+            check(lib.dmoq_combine_weighted(C.byref(ws.route), ptr(ws.dn), self.hidden, ptr(y), is_bf16, s),
+                  "dmoq_combine_weighted")
+            mark("combine")
+            return y
         # pool by pool: gate_up + SiLU, down-side rotation, down.  The down-side code / scale scratch and the transient
         # weight image are shared by all pools; stream order makes each consumer finish before the next producer writes
         for i, p in enumerate(self.pools):

@@ -274,6 +274,23 @@ int dmoq_widen_indices(const uint8_t* packed, int64_t n_bytes, int32_t bit, uint
  * the norm image holds G*N floats.  Reads pool->{gu,dn}_{idx,norm,lut}, bit, mode, identity_lut, n_members, inter.
  */
 /*
+ * Small-batch (decode) path of the WxA16 layer: two streaming launches that cover ALL pools of a layer whose routing
+ * tables were built with tile_m = 32.  The packed indices are read from global memory as they are stored, looked up in
+ * registers and multiplied with warp-level MMAs whose M operand is the weights, so a tile of a few routed rows does not
+ * pay for 128.  Same math as dmoq_grouped_gemm in A16 mode (turboquant_utils/triton_kernels.py:1375, small-batch tile
+ * class :475-510; SiLU*up of quantization/wxa16/bit_partitioned_moe.py:925-931).
+ *   gateup: reads every pool's rotated fp16 activations (pool.act_codes, rows through route->a_row) and writes
+ *           act (R, act_stride) fp16 = silu(gate) * up
+ *   down:   reads the rotated SiLU outputs a_rot (R, a_stride) fp16 of dmoq_rotate_quant_down and writes plain fp16
+ *           rows dn (R, hidden) for dmoq_combine_weighted
+ * Pools must be A16 with bit 1, 2, 4, or 8 with the uniform codebook; hidden a multiple of 256.
+ */
+int dmoq_moe_decode_gateup(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t n_pools, int32_t hidden,
+                           uint16_t* act, int32_t act_stride, void* stream);
+int dmoq_moe_decode_down(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t n_pools, int32_t hidden,
+                         const uint16_t* a_rot, int32_t a_stride, uint16_t* dn, void* stream);
+
+/*
  * Rows of a pool's activation-code table put into routed-row order: for every row r of the pool's tiles,
  * dst row r = src row route->a_row[r] (row_bytes of codes, scale_bytes of scales; the scale pointers may both be
  * NULL).  After it the pool's GEMM can take whole 128-row tiles of the table with tensor-map copies; it then gets a
