@@ -306,7 +306,8 @@ class CodesExchange:
         if self._pool_of is None:
             self._pool_of = eng.expert_pool.cpu().numpy()[:self.E_loc]
             self._rank_of = eng.expert_rank.cpu().numpy()[:self.E_loc]
-        n_chunks = max(1, min(self.n_chunks, self.E_loc))
+        # small exchanges go in one piece: a block must be worth its collective's launch latency
+        n_chunks = max(1, min(self.n_chunks if ws.R >= 65536 else 1, self.E_loc))
         edges = [self.E_loc * c // n_chunks for c in range(n_chunks + 1)]
         send_start = np.concatenate([[0], np.cumsum(send_c.reshape(-1))])     # first routed row of every global expert
         keep = []
