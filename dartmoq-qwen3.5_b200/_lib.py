@@ -76,6 +76,8 @@ EXPORTS = {
                                          C.c_void_p]),
     "dmoq_moe_decode_down": (C.c_int, [C.POINTER(Route), C.POINTER(Pool), C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
                                        C.c_void_p, C.c_void_p]),
+    "dmoq_quantize_packed": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                       C.c_void_p, C.c_void_p, C.c_void_p]),
     "dmoq_gather_rows": (C.c_int, [C.POINTER(Route), C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
                                    C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "dmoq_weight_image_bytes": (C.c_size_t, [C.POINTER(Pool), C.c_int32, C.c_int32]),

@@ -353,3 +353,34 @@ def wxfp4_matmul_merged_in_features_gf(x_f4_t, x_s, indices_packed_gf, nib, w_s,
     a = x_f4_t.t().contiguous()
     return _merged(FP4, True, a, x_s.contiguous(), a.shape[1] * 2, indices_packed_gf, nib.contiguous(), norms_gf,
                    expert_info, group_size, bit_width, norms_prescaled, e0=_fp4_e0(w_s), **kw)
+
+
+
+@_on_tensor_device
+def quantize_packed_full(W: torch.Tensor, bit_width: int, group_size: int = GROUP, seed: int = 42,
+                         uniform_codebook: bool = False) -> dict:
+    """``format.turboquant_quantize_packed_full`` (turboquant_utils/quantize.py:350) as one library kernel: the same
+    dict, tensors on W's device.  Rotation matrices and codebook come from the format module (the reference's own
+    CPU generators), the per-element work runs in ``dmoq_quantize_packed``."""
+    _need_cuda(W)
+    if bit_width not in fmt.SUPPORTED_BITS:
+        raise ValueError(f"bit_width must be 1/2/4/8, got {bit_width}")
+    if group_size != GROUP or W.shape[1] % GROUP:
+        raise ValueError(f"group_size must be {GROUP} and K a multiple of it")
+    if uniform_codebook and bit_width != 8:
+        raise ValueError(f"uniform_codebook requires bit_width=8, got {bit_width}")
+    kind = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}.get(W.dtype)
+    if kind is None:
+        raise TypeError(f"W must be fp32, fp16 or bf16, got {W.dtype}")
+    W = W.contiguous()
+    N, K = W.shape
+    cent, edges = fmt.uniform8_codebook() if uniform_codebook else fmt.get_codebook(bit_width)
+    rot = torch.stack([fmt.generate_rotation_matrix(GROUP, seed=seed + g0) for g0 in range(0, K, GROUP)]).to(W.device).float().contiguous()
+    edges_d = edges.to(W.device).float().contiguous()
+    idx = torch.empty((N, K * bit_width // 8), dtype=torch.uint8, device=W.device)
+    norms = torch.empty((N, K // GROUP), dtype=torch.float16, device=W.device)
+    check(_lib.load().dmoq_quantize_packed(ptr(W), kind, N, K, bit_width, ptr(rot), ptr(edges_d), ptr(idx), ptr(norms),
+                                           _stream()), "dmoq_quantize_packed")
+    return {"indices_packed": idx, "codebook": cent.half().cpu(), "norms": norms, "seed": seed, "group_size": GROUP,
+            "shape": (N, K), "bit_width": bit_width, "rotation": "qr", "orig_dtype": str(W.dtype),
+            "codebook_type": "uniform" if uniform_codebook else "lloydmax"}

@@ -306,6 +306,18 @@ size_t dmoq_weight_image_bytes(const dmoq_pool_t* pool, int32_t is_down, int32_t
 int dmoq_expand_weights(const dmoq_pool_t* pool, int32_t is_down, int32_t hidden, void* image, float* norm_image,
                         void* stream);
 
+/*
+ * Offline quantiser of the packed format (turboquant_utils/quantize.py:350-472, group size 128): per group and row the
+ * L2 norm, the rotated normalised row scaled by sqrt(128), its codebook cell (torch.searchsorted over the cell edges),
+ * packed little-endian within each byte.
+ *   w (N, K) row-major, w_kind 0 fp32 / 1 fp16 / 2 bf16;  rot (K/128, 128, 128) fp32, matrix of group g from seed + g*128
+ *   (rotation.py:53);  edges (2^bit - 1) fp32;  indices_packed (N, K*bit/8) u8;  norms (N, K/128) fp16
+ * fp32 arithmetic in a fixed order; an index can differ from a BLAS-ordered evaluation only where a value lies within
+ * rounding of a cell edge.
+ */
+int dmoq_quantize_packed(const void* w, int32_t w_kind, int32_t N, int32_t K, int32_t bit, const float* rot,
+                         const float* edges, uint8_t* indices_packed, uint16_t* norms, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

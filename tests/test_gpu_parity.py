@@ -594,6 +594,34 @@ def test_expert_parallel_building_blocks_on_one_gpu(mode):
     assert rel_fro(alone.float().cpu(), dense) < 2e-2
 
 
+@pytest.mark.parametrize("b", (1, 2, 4, 8))
+def test_quantizer_kernel_vs_reference_golden(golden, b):
+    """The quantiser as a library kernel on the reference's own input: norms and indices equal the reference's
+    (torch CPU) outputs except where a rotated value sits within fp32 rounding of a cell edge or a norm within rounding
+    of an fp16 midpoint (the kernel sums in a fixed order, torch's BLAS in its own); the dequantised matrix agrees."""
+    g = golden("quantizer")
+    W = torch.from_numpy(g["W"])
+    pk = K.quantize_packed_full(W.to(DEV), b, 128, seed=42 + b)
+    got = F.unpack_nbit(pk["indices_packed"].cpu(), b, W.shape[1]).numpy()
+    want = F.unpack_nbit(torch.from_numpy(g[f"idx_{b}"]), b, W.shape[1]).numpy()
+    differ = got != want
+    assert differ.mean() < 2e-4, differ.mean()
+    assert (np.abs(got.astype(np.int32) - want.astype(np.int32))[differ] <= 1).all()      # only neighbouring cells
+    n_got, n_want = pk["norms"].cpu().numpy(), g[f"norms_{b}"]
+    assert (n_got != n_want).mean() < 5e-3 and np.allclose(n_got.astype(np.float32), n_want.astype(np.float32), rtol=1e-3)
+    assert np.array_equal(pk["codebook"].numpy(), g[f"cb_{b}"])
+    deq = F.turboquant_dequantize_packed(dict(pk, orig_dtype="torch.float32"), device="cpu").numpy()
+    assert rel_fro(deq, g[f"deq_{b}"]) < 2e-3
+    # bf16 input and an input that is not a multiple of the row block
+    W2 = synth.make_activations(70, 256, seed=4).to(DEV)
+    p2 = K.quantize_packed_full(W2, b, 128, seed=7)
+    r2 = F.turboquant_quantize_packed_full(W2.cpu(), b, 128, seed=7)
+    i2, j2 = F.unpack_nbit(p2["indices_packed"].cpu(), b, 256), F.unpack_nbit(r2["indices_packed"], b, 256)
+    assert (i2 != j2).float().mean() < 2e-4
+    with pytest.raises(ValueError):
+        K.quantize_packed_full(W2, 3)
+
+
 def test_zz_tensor_core_status_word_is_clean():
     """No bounded wait of the tcgen05 kernels ran out during this session."""
     import ctypes
