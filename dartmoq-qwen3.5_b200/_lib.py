@@ -67,6 +67,9 @@ EXPORTS = {
     "dmoq_grouped_gemm": (C.c_int, [C.POINTER(Route), C.POINTER(Pool), C.c_int32, C.c_int32, C.c_int32,
                                     C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32,
                                     C.c_void_p, C.c_void_p]),
+    "dmoq_grouped_gemm_pools": (C.c_int, [C.POINTER(Route), C.POINTER(Pool), C.POINTER(C.c_int32), C.c_int32, C.c_int32,
+                                          C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32,
+                                          C.c_void_p]),
     "dmoq_tc_status": (C.c_int, [C.POINTER(C.c_int32)]),
     "dmoq_combine": (C.c_int, [C.POINTER(Route), C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "dmoq_combine_weighted": (C.c_int, [C.POINTER(Route), C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),

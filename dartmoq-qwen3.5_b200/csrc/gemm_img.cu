@@ -84,13 +84,27 @@ struct Cfg {
                 "role register budgets exceed the block's register pool");
 };
 
+// One launch covers the tiles of up to DMOQ_MAX_POOLS pools of one activation mode (the kernel never looks at bit
+// widths: the images hold codewords).  Per pool: its image (tensor map), norms, sizes and tile list.
+struct ImgPool {
+  const float* norm_img;      // (groups, n_img) fp32, image row order
+  int n_img;                  // image rows per group
+  int inter;                  // intermediate size of the pool's members
+  int pool;                   // index into the routing tables' per-pool tile lists
+};
+
+struct ImgMaps {
+  CUtensorMap a;                     // the activation-code table in routed-row order
+  CUtensorMap b[DMOQ_MAX_POOLS];     // one weight image per pool of the launch
+};
+
 struct ImgArgs {
   const DmoqTile* tiles;
   const int32_t* n_tiles;
   const float* row_weight;
-  int pool, is_down, inter, hidden;
-  const float* norm_img;      // (groups, n_img) fp32, image row order
-  int n_img;                  // image rows per group
+  ImgPool pp[DMOQ_MAX_POOLS];
+  int n_pp;
+  int is_down, hidden;
   const uint8_t* a_scales;    // A8/FP8: fp16 (rows, K/128); FP4: e8m0 bytes (rows, K/32); row r of the table feeds row r
   int a_stride;               // row pitch of the code table in elements (the codes themselves come through tmap_a)
   void* out;
@@ -259,8 +273,8 @@ struct Shape {
 };
 
 template <int MODE, int EPI, int BN>
-__global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                                                                        const __grid_constant__ CUtensorMap tmap_b, ImgArgs a) {
+__global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __grid_constant__ ImgMaps maps,
+                                                                        const __grid_constant__ ImgArgs a) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   Smem<BN>& S = *reinterpret_cast<Smem<BN>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -312,19 +326,52 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
     tc_fence_after();
   }
 
-  const int n_tiles = a.n_tiles[a.pool];
-  const DmoqTile* tiles = a.tiles + a.n_tiles[DMOQ_MAX_POOLS + a.pool];
-  const int NB = a.is_down ? a.hidden / BN : a.inter / (BN / 2);
-  const int G = a.is_down ? a.inter / kG : a.hidden / kG;
-  const int steps_per_item = (G * SPG + GPS - 1) / GPS;
-  const int n_work = n_tiles * NB;
+  // Work items = (tile, column block) pairs of every pool of the launch, pool after pool; CTA b takes items b, b + grid, ...
+  // Every role walks the same list, so each computes an item's pool, tile and group count for itself.
+  int work_end[DMOQ_MAX_POOLS];       // exclusive prefix of the pools' item counts
+  int n_work = 0;
+#pragma unroll
+  for (int q = 0; q < DMOQ_MAX_POOLS; ++q) {
+    if (q < a.n_pp) {
+      const int nbq = a.is_down ? a.hidden / BN : a.pp[q].inter / (BN / 2);
+      n_work += a.n_tiles[a.pp[q].pool] * nbq;
+    }
+    work_end[q] = n_work;
+  }
   const int stride_w = gridDim.x;
   const int n_items = (int)blockIdx.x < n_work ? (n_work - 1 - (int)blockIdx.x) / stride_w + 1 : 0;
-  const DmoqTile kNoTile{0, 0, 0, 0};
-  auto tile_of = [&](int item) {   // item index of this CTA -> tile record (clamped past the end)
-    const int w = blockIdx.x + item * stride_w;
-    return (item < n_items) ? tiles[w / NB] : kNoTile;
+  struct Item {
+    DmoqTile tile;
+    int q, nb, G;
   };
+  auto pool_of_item = [&](int item, int& start) {   // which pool of the launch the CTA's item-th work item belongs to
+    const int w = blockIdx.x + item * stride_w;
+    int q = 0;
+    start = 0;
+#pragma unroll
+    for (int j = 0; j < DMOQ_MAX_POOLS - 1; ++j)
+      if (j + 1 < a.n_pp && w >= work_end[j]) {
+        q = j + 1;
+        start = work_end[j];
+      }
+    return q;
+  };
+  auto groups_of = [&](int q) { return a.is_down ? a.pp[q].inter / kG : a.hidden / kG; };
+  auto item_of = [&](int item) {   // item index of this CTA -> pool, tile record, column block (an empty tile past the end)
+    Item it_{DmoqTile{0, 0, 0, 0}, 0, 0, 1};
+    if (item < n_items) {
+      int start;
+      const int q = pool_of_item(item, start);
+      const int nbq = a.is_down ? a.hidden / BN : a.pp[q].inter / (BN / 2);
+      const int local = blockIdx.x + item * stride_w - start;
+      it_.q = q;
+      it_.nb = local % nbq;
+      it_.tile = a.tiles[a.n_tiles[DMOQ_MAX_POOLS + a.pp[q].pool] + local / nbq];
+      it_.G = groups_of(q);
+    }
+    return it_;
+  };
+  auto steps_of = [&](int G) { return (G * SPG + GPS - 1) / GPS; };
 
   if (warp < kEpiWarps) {
     // =========================================================================== epilogue warps
@@ -337,15 +384,16 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
     uint32_t ia = 0;                                 // groups consumed so far
     uint32_t v[2][8];                                // accumulator chunks: one in the scale math, one in flight
     bool prefetched = false;                         // the upcoming group's first chunk is already on its way
-    DmoqTile next = tile_of(0);
+    Item next = item_of(0);
     PROF_DECL;
 #ifdef DMOQ_IMG_PROFILE
     const long long prof_start = clock64();
 #endif
     for (int item = 0; item < n_items; ++item) {
-      const DmoqTile tile = next;
-      next = tile_of(item + 1);
-      const int nb = (blockIdx.x + item * stride_w) % NB;
+      const Item cur = next;
+      next = item_of(item + 1);
+      const DmoqTile tile = cur.tile;
+      const int nb = cur.nb, G = cur.G, inter = a.pp[cur.q].inter;
       const bool live = row < tile.rows;
       // row scales: this row's G fp16 values, fetched four at a time (8-byte loads, one block ahead) where the row
       // pitch allows, else one at a time
@@ -439,12 +487,12 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
             }
           }
           if (BN == 128 && MODE == DMOQ_A8 && a.partials != nullptr && live) {   // parity checks only (128-column tiles)
-            const int n_out = a.is_down ? a.hidden : 2 * a.inter;
+            const int n_out = a.is_down ? a.hidden : 2 * inter;
 #pragma unroll
             for (int j = 0; j < CW; ++j) {
               const int col = CW * c + j;                                        // 0..31
               const int n = a.is_down ? nb * BN + cbase + col
-                                      : (col < 16 ? 0 : a.inter) + nb * (BN / 2) + cq * 16 + (col & 15);
+                                      : (col < 16 ? 0 : inter) + nb * (BN / 2) + cq * 16 + (col & 15);
               a.partials[((size_t)(tile.row0 + row) * n_out + n) * G + g] = (int32_t)(vc[j] - kMagicBits);
             }
           }
@@ -504,7 +552,7 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
               for (int q = 0; q < 4; ++q) dst[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
             } else {   // plain gate_up rows: [gate | up], each inter wide
               uint4* dg = reinterpret_cast<uint4*>(orow + nb * (BN / 2) + (cq * NH + h) * 16);
-              uint4* du = reinterpret_cast<uint4*>(orow + a.inter + nb * (BN / 2) + (cq * NH + h) * 16);
+              uint4* du = reinterpret_cast<uint4*>(orow + inter + nb * (BN / 2) + (cq * NH + h) * 16);
               dg[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
               dg[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
               du[0] = make_uint4(pk[8], pk[9], pk[10], pk[11]);
@@ -532,13 +580,16 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
 #ifdef DMOQ_IMG_PROFILE
       const long long prof_start = clock64();
 #endif
-      DmoqTile t_next = tile_of(0);
+      Item t_next = item_of(0);
       for (int item = 0; item < n_items; ++item) {
-        const DmoqTile tile = t_next;
-        t_next = tile_of(item + 1);
-        const int nb = (blockIdx.x + item * stride_w) % NB;
+        const Item cur = t_next;
+        t_next = item_of(item + 1);
+        const DmoqTile tile = cur.tile;
+        const ImgPool& pp = a.pp[cur.q];
+        const int nb = cur.nb, G = cur.G;
         const int gg0 = a.is_down ? tile.rank * G : 0;                       // first image group of this item
-        const int img_row0 = a.is_down ? nb * BN : tile.rank * 2 * a.inter + nb * BN;
+        const int img_row0 = a.is_down ? nb * BN : tile.rank * 2 * pp.inter + nb * BN;
+        const int steps_per_item = steps_of(G);
         for (int st = 0; st < steps_per_item; ++st, ++it) {
           const int s = it % kStages;
           PROF_BEGIN();
@@ -555,18 +606,18 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
               int x, y;
               if (MODE == DMOQ_A16) {
                 x = (st & 1) * 128;
-                y = (gg0 + (st >> 1)) * a.n_img + img_row0;
+                y = (gg0 + (st >> 1)) * pp.n_img + img_row0;
               } else if (MODE == DMOQ_FP4) {
                 x = 0;
-                y = ((gg0 >> 1) + st) * a.n_img + img_row0;   // two groups per image row group; gg0 is even (checked on the host)
+                y = ((gg0 >> 1) + st) * pp.n_img + img_row0;   // two groups per image row group; gg0 is even (checked on the host)
               } else {
                 x = 0;
-                y = (gg0 + st) * a.n_img + img_row0;
+                y = (gg0 + st) * pp.n_img + img_row0;
               }
-              tma_load_2d(&S.a[s][0], &tmap_a, st * 128, tile.row0, &S.full[s]);
-              tma_load_2d(&S.b[s][0], &tmap_b, x, y, &S.full[s]);
+              tma_load_2d(&S.a[s][0], &maps.a, st * 128, tile.row0, &S.full[s]);
+              tma_load_2d(&S.b[s][0], &maps.b[cur.q], x, y, &S.full[s]);
               for (int j = 0; j < n_groups; ++j, ++ig)
-                bulk_g2s(&S.norm[ig % kNormRing][0], a.norm_img + (size_t)(gg0 + g_first + j) * a.n_img + img_row0, BN * 4, &S.full[s]);
+                bulk_g2s(&S.norm[ig % kNormRing][0], pp.norm_img + (size_t)(gg0 + g_first + j) * pp.n_img + img_row0, BN * 4, &S.full[s]);
             } else {
               mbar_arrive(&S.full[s]);   // keep the arrival count whole after an abort
             }
@@ -614,6 +665,9 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
       const long long prof_start = clock64();
 #endif
       for (int item = 0; item < n_items; ++item) {
+        int start_unused;
+        const int G = groups_of(pool_of_item(item, start_unused));
+        const int steps_per_item = steps_of(G);
         for (int st = 0; st < steps_per_item; ++st, ++it) {
           const int s = it % kStages;
           PROF_BEGIN();
@@ -713,7 +767,7 @@ int make_image_map(CUtensorMap* map, const void* image, size_t rows, size_t row_
 }
 
 template <int MODE, int EPI, int BN>
-int launch(const CUtensorMap& map_a, const CUtensorMap& map, const ImgArgs& a, int work_cap, cudaStream_t s) {
+int launch(const ImgMaps& maps, const ImgArgs& a, int work_cap, cudaStream_t s) {
   static DmoqOncePerDevice once;
   bool* configured = once.slot();
   if (configured == nullptr) return DMOQ_EDEVICE;
@@ -729,16 +783,16 @@ int launch(const CUtensorMap& map_a, const CUtensorMap& map, const ImgArgs& a, i
   int grid = dmoq_sm_count();
   if (grid > work_cap) grid = work_cap;
   if (grid < 1) grid = 1;
-  gemm_img_kernel<MODE, EPI, BN><<<grid, Cfg<BN>::kThreads, bytes, s>>>(map_a, map, a);
+  gemm_img_kernel<MODE, EPI, BN><<<grid, Cfg<BN>::kThreads, bytes, s>>>(maps, a);
   return dmoq_launch_status();
 }
 
 template <int MODE, int BN>
-int launch_epi(const CUtensorMap& map_a, const CUtensorMap& map, const ImgArgs& a, int epi, int work_cap, cudaStream_t s) {
+int launch_epi(const ImgMaps& maps, const ImgArgs& a, int epi, int work_cap, cudaStream_t s) {
   switch (epi) {
-    case DMOQ_EPI_SILU: return launch<MODE, DMOQ_EPI_SILU, BN>(map_a, map, a, work_cap, s);
-    case DMOQ_EPI_WEIGHTED: return launch<MODE, DMOQ_EPI_WEIGHTED, BN>(map_a, map, a, work_cap, s);
-    case DMOQ_EPI_PLAIN: return launch<MODE, DMOQ_EPI_PLAIN, BN>(map_a, map, a, work_cap, s);
+    case DMOQ_EPI_SILU: return launch<MODE, DMOQ_EPI_SILU, BN>(maps, a, work_cap, s);
+    case DMOQ_EPI_WEIGHTED: return launch<MODE, DMOQ_EPI_WEIGHTED, BN>(maps, a, work_cap, s);
+    case DMOQ_EPI_PLAIN: return launch<MODE, DMOQ_EPI_PLAIN, BN>(maps, a, work_cap, s);
     default: return DMOQ_EINVAL;
   }
 }
@@ -755,57 +809,77 @@ bool dmoq_img_supported(const dmoq_pool_t& p, int is_down, int hidden) {
   return true;   // the caller also needs the code table in routed-row order (route->a_row == NULL, or the down side)
 }
 
-int dmoq_grouped_gemm_img(const dmoq_route_t* route, const dmoq_pool_t& p, int pool_index, int is_down, int epilogue,
-                          int hidden, const void* a_codes, const void* a_scales, int a_stride, void* out, int out_stride,
-                          int32_t* partials, cudaStream_t s) {
+// One launch over the listed pools (all of one activation mode, each with a weight image for this projection).
+int dmoq_grouped_gemm_img_pools(const dmoq_route_t* route, const dmoq_pool_t* pools, const int32_t* pool_ids, int n_ids,
+                                int is_down, int epilogue, int hidden, const void* a_codes, const void* a_scales, int a_stride,
+                                void* out, int out_stride, int32_t* partials, cudaStream_t s) {
+  if (n_ids < 1 || n_ids > DMOQ_MAX_POOLS) return DMOQ_EINVAL;
+  const int mode = pools[pool_ids[0]].mode;
+  if (mode == DMOQ_FP4 && n_ids != 1) return DMOQ_EINVAL;   // the weight block scale in TMEM is one pool's
   ImgArgs a{};
+  ImgMaps maps;
   a.tiles = reinterpret_cast<const DmoqTile*>(route->tiles);
   a.n_tiles = route->n_tiles;
   a.row_weight = route->sorted_weights;
-  a.pool = pool_index;
+  a.n_pp = n_ids;
   a.is_down = is_down;
-  a.inter = p.inter;
   a.hidden = hidden;
-  a.norm_img = is_down ? p.dn_norm_img : p.gu_norm_img;
-  a.n_img = is_down ? hidden : p.n_members * 2 * p.inter;
   a.a_scales = static_cast<const uint8_t*>(a_scales);
   a.a_stride = a_stride;
   a.out = out;
   a.out_stride = out_stride;
   a.partials = partials;
-  const int e0 = is_down ? p.dn_e0 : p.gu_e0;
-  a.sfb_word = 0x01010101u * (uint32_t)((127 + e0) & 0xFF);
-  const int groups = is_down ? p.n_members * p.inter / kG : hidden / kG;
-  // image geometry: rows of 128 elements (256 bytes as fp16, 128 bytes otherwise); e2m1 rows hold two groups
-  size_t rows, row_bytes;
-  if (p.mode == DMOQ_FP4) {
-    rows = (size_t)((groups + 1) / 2) * a.n_img;
-    row_bytes = 128;
-  } else {
-    rows = (size_t)groups * a.n_img;
-    row_bytes = (p.mode == DMOQ_A16) ? 256 : 128;
-  }
   // 256-column tiles wherever the shape allows (not FP4: its scale-factor columns share TMEM with the accumulators)
-  const bool wide = p.mode != DMOQ_FP4 && partials == nullptr && (is_down ? hidden % 256 == 0 : p.inter % 128 == 0);
+  bool wide = mode != DMOQ_FP4 && partials == nullptr && (is_down ? hidden % 256 == 0 : true);
+  for (int i = 0; i < n_ids; ++i) wide = wide && (is_down || pools[pool_ids[i]].inter % 128 == 0);
   const int bn = wide ? 256 : 128;
-  CUtensorMap map, map_a;
-  int rc = make_image_map(&map, is_down ? p.dn_img : p.gu_img, rows, row_bytes, bn);
-  if (rc != DMOQ_OK) return rc;
+  long long cap = 0;
+  for (int i = 0; i < n_ids; ++i) {
+    const dmoq_pool_t& p = pools[pool_ids[i]];
+    if (p.mode != mode || !dmoq_img_supported(p, is_down, hidden)) return DMOQ_EINVAL;
+    ImgPool& pp = a.pp[i];
+    pp.norm_img = is_down ? p.dn_norm_img : p.gu_norm_img;
+    pp.n_img = is_down ? hidden : p.n_members * 2 * p.inter;
+    pp.inter = p.inter;
+    pp.pool = pool_ids[i];
+    const int groups = is_down ? p.n_members * p.inter / kG : hidden / kG;
+    // image geometry: rows of 128 elements (256 bytes as fp16, 128 bytes otherwise); e2m1 rows hold two groups
+    size_t rows, row_bytes;
+    if (mode == DMOQ_FP4) {
+      rows = (size_t)((groups + 1) / 2) * pp.n_img;
+      row_bytes = 128;
+      const int e0 = is_down ? p.dn_e0 : p.gu_e0;
+      a.sfb_word = 0x01010101u * (uint32_t)((127 + e0) & 0xFF);
+    } else {
+      rows = (size_t)groups * pp.n_img;
+      row_bytes = (mode == DMOQ_A16) ? 256 : 128;
+    }
+    const int rc = make_image_map(&maps.b[i], is_down ? p.dn_img : p.gu_img, rows, row_bytes, bn);
+    if (rc != DMOQ_OK) return rc;
+    cap += (long long)route->tile_cap * (is_down ? hidden / bn : p.inter / (bn / 2));
+  }
+  for (int i = n_ids; i < DMOQ_MAX_POOLS; ++i) maps.b[i] = maps.b[0];
   // the activation-code table: one row per routed row, in routed-row order
   const size_t a_rows = (size_t)route->T * route->top_k + (route->has_shared ? (size_t)route->T : 0);
-  const size_t a_pitch = (p.mode == DMOQ_A16) ? (size_t)a_stride * 2 : (p.mode == DMOQ_FP4) ? (size_t)a_stride / 2 : (size_t)a_stride;
-  rc = make_image_map(&map_a, a_codes, a_rows, a_pitch, 128);
+  const size_t a_pitch = (mode == DMOQ_A16) ? (size_t)a_stride * 2 : (mode == DMOQ_FP4) ? (size_t)a_stride / 2 : (size_t)a_stride;
+  const int rc = make_image_map(&maps.a, a_codes, a_rows, a_pitch, 128);
   if (rc != DMOQ_OK) return rc;
-  const int nb = is_down ? hidden / bn : p.inter / (bn / 2);
-  long long cap = (long long)route->tile_cap * nb;
   const int work_cap = cap > (1 << 30) ? (1 << 30) : (int)cap;
-  switch (p.mode) {
-    case DMOQ_A16: return wide ? launch_epi<DMOQ_A16, 256>(map_a, map, a, epilogue, work_cap, s) : launch_epi<DMOQ_A16, 128>(map_a, map, a, epilogue, work_cap, s);
-    case DMOQ_A8: return wide ? launch_epi<DMOQ_A8, 256>(map_a, map, a, epilogue, work_cap, s) : launch_epi<DMOQ_A8, 128>(map_a, map, a, epilogue, work_cap, s);
-    case DMOQ_FP8: return wide ? launch_epi<DMOQ_FP8, 256>(map_a, map, a, epilogue, work_cap, s) : launch_epi<DMOQ_FP8, 128>(map_a, map, a, epilogue, work_cap, s);
-    case DMOQ_FP4: return launch_epi<DMOQ_FP4, 128>(map_a, map, a, epilogue, work_cap, s);
+  switch (mode) {
+    case DMOQ_A16: return wide ? launch_epi<DMOQ_A16, 256>(maps, a, epilogue, work_cap, s) : launch_epi<DMOQ_A16, 128>(maps, a, epilogue, work_cap, s);
+    case DMOQ_A8: return wide ? launch_epi<DMOQ_A8, 256>(maps, a, epilogue, work_cap, s) : launch_epi<DMOQ_A8, 128>(maps, a, epilogue, work_cap, s);
+    case DMOQ_FP8: return wide ? launch_epi<DMOQ_FP8, 256>(maps, a, epilogue, work_cap, s) : launch_epi<DMOQ_FP8, 128>(maps, a, epilogue, work_cap, s);
+    case DMOQ_FP4: return launch_epi<DMOQ_FP4, 128>(maps, a, epilogue, work_cap, s);
     default: return DMOQ_EINVAL;
   }
+}
+
+int dmoq_grouped_gemm_img(const dmoq_route_t* route, const dmoq_pool_t* pools, int pool_index, int is_down, int epilogue,
+                          int hidden, const void* a_codes, const void* a_scales, int a_stride, void* out, int out_stride,
+                          int32_t* partials, cudaStream_t s) {
+  const int32_t id = pool_index;
+  return dmoq_grouped_gemm_img_pools(route, pools, &id, 1, is_down, epilogue, hidden, a_codes, a_scales, a_stride, out,
+                                     out_stride, partials, s);
 }
 
 #ifdef DMOQ_IMG_PROFILE

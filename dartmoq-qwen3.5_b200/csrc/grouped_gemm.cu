@@ -538,9 +538,12 @@ int dmoq_grouped_gemm_tc(const dmoq_route_t* route, const dmoq_pool_t& p, int po
                          int32_t* partials, cudaStream_t s);
 
 bool dmoq_img_supported(const dmoq_pool_t& p, int is_down, int hidden);
-int dmoq_grouped_gemm_img(const dmoq_route_t* route, const dmoq_pool_t& p, int pool_index, int is_down, int epilogue,
+int dmoq_grouped_gemm_img(const dmoq_route_t* route, const dmoq_pool_t* pools, int pool_index, int is_down, int epilogue,
                           int hidden, const void* a_codes, const void* a_scales, int a_stride, void* out, int out_stride,
                           int32_t* partials, cudaStream_t s);
+int dmoq_grouped_gemm_img_pools(const dmoq_route_t* route, const dmoq_pool_t* pools, const int32_t* pool_ids, int n_ids,
+                                int is_down, int epilogue, int hidden, const void* a_codes, const void* a_scales, int a_stride,
+                                void* out, int out_stride, int32_t* partials, cudaStream_t s);
 
 // DMOQ_GEMM=mma forces the warp-level MMA kernel for every pool (A/B comparisons); default picks the
 // tcgen05 kernel wherever it applies.
@@ -573,7 +576,7 @@ extern "C" int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* p
   // a pool that comes with a weight image runs on the image-fed tensor-core kernel, which takes whole tiles of the
   // activation-code table: the table must be in routed-row order
   if (route->tile_m == 128 && use_tc_path() && (is_down || route->a_row == nullptr) && dmoq_img_supported(p, is_down, hidden))
-    return dmoq_grouped_gemm_img(route, p, pool_index, is_down, epilogue, hidden, a_codes, a_scales, a_stride, out,
+    return dmoq_grouped_gemm_img(route, pools_host, pool_index, is_down, epilogue, hidden, a_codes, a_scales, a_stride, out,
                                  out_stride, partials, static_cast<cudaStream_t>(stream));
   if (route->tile_m == 128 && use_tc_path() && dmoq_tc_supported(p, is_down, hidden))
     return dmoq_grouped_gemm_tc(route, p, pool_index, is_down, epilogue, hidden, a_codes, a_scales, a_stride, out,
@@ -614,4 +617,24 @@ extern "C" int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* p
     case DMOQ_FP4: return launch_bit<DMOQ_FP4>(a, p.bit, epilogue, route->tile_m, work_cap, s);
     default: return DMOQ_EINVAL;
   }
+}
+
+// The same GEMM for several pools of one activation mode in ONE launch; every listed pool needs its weight image
+// and the code table must be in routed-row order.
+extern "C" int dmoq_grouped_gemm_pools(const dmoq_route_t* route, const dmoq_pool_t* pools_host, const int32_t* pool_ids,
+                                       int32_t n_ids, int32_t is_down, int32_t epilogue, int32_t hidden,
+                                       const void* a_codes, const void* a_scales, int32_t a_stride, void* out,
+                                       int32_t out_stride, void* stream) {
+  DMOQ_CHECK_ARG(route && pools_host && pool_ids && a_codes && out && n_ids >= 1 && n_ids <= DMOQ_MAX_POOLS);
+  DMOQ_CHECK_ARG(route->tile_m == 128 && (is_down || route->a_row == nullptr));
+  DMOQ_CHECK_ARG(!(epilogue == DMOQ_EPI_SILU && is_down) && !(epilogue == DMOQ_EPI_WEIGHTED && !is_down));
+  DMOQ_CHECK_ARG(out_stride % 8 == 0 && hidden > 0 && hidden % kG == 0 && a_stride % kG == 0);
+  for (int i = 0; i < n_ids; ++i) {
+    DMOQ_CHECK_ARG(pool_ids[i] >= 0 && pool_ids[i] < route->n_pools);
+    const dmoq_pool_t& p = pools_host[pool_ids[i]];
+    DMOQ_CHECK_ARG(p.mode == DMOQ_A16 || a_scales);
+    DMOQ_CHECK_ARG(p.inter > 0 && p.inter % kG == 0 && a_stride >= (is_down ? p.inter : hidden));
+  }
+  return dmoq_grouped_gemm_img_pools(route, pools_host, pool_ids, n_ids, is_down, epilogue, hidden, a_codes, a_scales, a_stride,
+                                     out, out_stride, nullptr, static_cast<cudaStream_t>(stream));
 }

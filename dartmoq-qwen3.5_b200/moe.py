@@ -585,6 +585,44 @@ class _Engine:
                   "dmoq_combine_weighted")
             mark("combine")
             return y
+        img_modes = [self._image_mode(p, T, ws.tile_m) for p in self.pools]
+        merged = (partials is None and len(self.pools) > 1 and all(m == 1 for m in img_modes)
+                  and len({p.mode for p in self.pools}) == 1 and self.pools[0].mode != FP4)
+        if merged:
+            # every pool has a resident weight image and the same activation mode: one GEMM launch per projection walks
+            # the tile lists of all pools (small pools cost no launches of their own)
+            codes, scales, stride = self._sorted_tables(ws)
+            for i, p in enumerate(self.pools):
+                p.build_norm_images()
+                p.c.gu_img, p.c.dn_img = p.img[0].data_ptr(), p.img[1].data_ptr()
+                self.pool_array[i] = p.c
+                has_scales = p.scale_bytes(self.hidden) > 0
+                check(lib.dmoq_gather_rows(C.byref(ws.route), i, ptr(ws.act_codes[i]), p.code_bytes(self.hidden),
+                                           p.code_bytes(self.hidden), ptr(codes), p.code_bytes(stride),
+                                           ptr(ws.act_scales[i]) if has_scales else None, p.scale_bytes(self.hidden),
+                                           p.scale_bytes(self.hidden), ptr(scales) if has_scales else None,
+                                           p.scale_bytes(stride), s), "dmoq_gather_rows")
+            mark("gather")
+            ids = (C.c_int32 * len(self.pools))(*range(len(self.pools)))
+            check(lib.dmoq_grouped_gemm_pools(C.byref(ws.route_sorted), self.pool_array, ids, len(self.pools), 0, EPI_SILU,
+                                              self.hidden, ptr(codes), ptr(scales), stride, ptr(ws.act), self.inter_max, s),
+                  "dmoq_grouped_gemm_pools(gate_up)")
+            mark("gate_up_silu:all")
+            for i, p in enumerate(self.pools):
+                check(lib.dmoq_rotate_quant_down(C.byref(ws.route), self.pool_array, i, ptr(ws.act), self.inter_max,
+                                                 ptr(ws.dn_codes), ptr(ws.dn_scales), self.inter_max, s),
+                      "dmoq_rotate_quant_down")
+            mark("rotate_quant_down")
+            check(lib.dmoq_grouped_gemm_pools(C.byref(ws.route), self.pool_array, ids, len(self.pools), 1, EPI_PLAIN,
+                                              self.hidden, ptr(ws.dn_codes), ptr(ws.dn_scales), self.inter_max,
+                                              ptr(ws.dn), self.hidden, s), "dmoq_grouped_gemm_pools(down)")
+            mark("down:all")
+            self.last_launches = (1 if T * self.k_v <= 1024 and T <= 4096 else 3) + 3 * len(self.pools) + 3
+            y = torch.empty_like(x)
+            check(lib.dmoq_combine_weighted(C.byref(ws.route), ptr(ws.dn), self.hidden, ptr(y), is_bf16, s),
+                  "dmoq_combine_weighted")
+            mark("combine")
+            return y
         # pool by pool: gate_up + SiLU, down-side rotation, down.  The down-side code / scale scratch and the transient
         # weight image are shared by all pools; stream order makes each consumer finish before the next producer writes
         for i, p in enumerate(self.pools):

@@ -223,6 +223,17 @@ int dmoq_grouped_gemm(const dmoq_route_t* route, const dmoq_pool_t* pools_host, 
                       void* out, int32_t out_stride, int32_t* partials, void* stream);
 
 /*
+ * dmoq_grouped_gemm over several pools of ONE activation mode in a single launch (their tile lists are walked one
+ * after the other by the same persistent kernel).  Every listed pool needs its weight image (gu_img / dn_img and the
+ * norm image); a_codes / a_scales is one table in routed-row order holding all these pools' rows (route->a_row NULL
+ * on the gate_up side).  Small pools then cost no launch of their own.  pool_ids is a HOST array.
+ */
+int dmoq_grouped_gemm_pools(const dmoq_route_t* route, const dmoq_pool_t* pools_host, const int32_t* pool_ids_host,
+                            int32_t n_ids, int32_t is_down, int32_t epilogue, int32_t hidden,
+                            const void* a_codes, const void* a_scales, int32_t a_stride,
+                            void* out, int32_t out_stride, void* stream);
+
+/*
  * Status word of the tensor-core (tcgen05) GEMM kernels on the current device, copied to the host
  * (synchronises the device).  0 = healthy; bit 0 = a bounded mbarrier wait ran out, the launch that hit
  * it wrote unspecified output.  No reference counterpart: the reference has no device-side waits.
