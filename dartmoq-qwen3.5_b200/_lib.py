@@ -75,6 +75,10 @@ EXPORTS = {
     "dmoq_combine_weighted": (C.c_int, [C.POINTER(Route), C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "dmoq_convert_group_first": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "dmoq_widen_indices": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
+    "dmoq_moe_decode_rotate": (C.c_int, [C.POINTER(Route), C.POINTER(Pool), C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
+                                         C.c_void_p]),
+    "dmoq_moe_decode_rotate_down": (C.c_int, [C.POINTER(Route), C.POINTER(Pool), C.c_int32, C.c_void_p, C.c_int32,
+                                              C.c_void_p, C.c_int32, C.c_void_p]),
     "dmoq_moe_decode_gateup": (C.c_int, [C.POINTER(Route), C.POINTER(Pool), C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
                                          C.c_void_p]),
     "dmoq_moe_decode_down": (C.c_int, [C.POINTER(Route), C.POINTER(Pool), C.c_int32, C.c_int32, C.c_void_p, C.c_int32,

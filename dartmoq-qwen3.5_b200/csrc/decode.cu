@@ -188,13 +188,16 @@ __device__ void run_tile(const DecArgs& a, const DecPool& P, const TileCtx& tc, 
 #pragma unroll
       for (int q = 0; q < 4; ++q) total[u][b][q] = 0.f;
 
+  // Codes and norms of the NEXT group travel in registers while the current group is computed (8-bit codes are 32
+  // bytes per row: those are loaded where they are used, the register file has no room for two groups of them).
+  constexpr bool kAhead = BIT < 8;
   Raw<BIT> nxt[2][2];
   uint16_t nrm_n[2][2];
 #pragma unroll
   for (int u = 0; u < 2; ++u)
 #pragma unroll
     for (int hi = 0; hi < 2; ++hi) {
-      nxt[u][hi] = load_raw<BIT>(idx_ptr(0, u, hi));
+      if (kAhead) nxt[u][hi] = load_raw<BIT>(idx_ptr(0, u, hi));
       nrm_n[u][hi] = P.norm[(size_t)gg0 * N + n_row[u] + 8 * hi];
     }
   stage(0, 0);
@@ -206,7 +209,7 @@ __device__ void run_tile(const DecArgs& a, const DecPool& P, const TileCtx& tc, 
     for (int u = 0; u < 2; ++u)
 #pragma unroll
       for (int hi = 0; hi < 2; ++hi) {
-        cur[u][hi] = nxt[u][hi];
+        if (kAhead) cur[u][hi] = nxt[u][hi];
         nrm[u][hi] = __half2float(__ushort_as_half(nrm_n[u][hi]));
       }
     if (g + 1 < G) {   // next group's codes, norms and activation tile are on their way during this group's math
@@ -214,7 +217,7 @@ __device__ void run_tile(const DecArgs& a, const DecPool& P, const TileCtx& tc, 
       for (int u = 0; u < 2; ++u)
 #pragma unroll
         for (int hi = 0; hi < 2; ++hi) {
-          nxt[u][hi] = load_raw<BIT>(idx_ptr(g + 1, u, hi));
+          if (kAhead) nxt[u][hi] = load_raw<BIT>(idx_ptr(g + 1, u, hi));
           nrm_n[u][hi] = P.norm[(size_t)(gg0 + g + 1) * N + n_row[u] + 8 * hi];
         }
       stage(g + 1, (g + 1) & 1);
@@ -225,18 +228,21 @@ __device__ void run_tile(const DecArgs& a, const DecPool& P, const TileCtx& tc, 
     __syncthreads();   // group g's activation tile is complete for every thread
     const uint8_t* xs = s_x + (g & 1) * (kRowsMax * kXPitch);
 
-    float acc[2][4][4];
 #pragma unroll
-    for (int u = 0; u < 2; ++u)
+    for (int u = 0; u < 2; ++u) {
+      float acc[4][4];
 #pragma unroll
       for (int b = 0; b < 4; ++b)
 #pragma unroll
-        for (int q = 0; q < 4; ++q) acc[u][b][q] = 0.f;
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
+        for (int q = 0; q < 4; ++q) acc[b][q] = 0.f;
       uint32_t h_lo[16], h_hi[16];   // codewords of rows rl and rl+8: 32 codes each, this thread's k positions 32*t4 ..
-      dequant32<BIT>(cur[u][0], h_lo, lut0, lut1, my_lut4, step2);
-      dequant32<BIT>(cur[u][1], h_hi, lut0, lut1, my_lut4, step2);
+      if (kAhead) {
+        dequant32<BIT>(cur[u][0], h_lo, lut0, lut1, my_lut4, step2);
+        dequant32<BIT>(cur[u][1], h_hi, lut0, lut1, my_lut4, step2);
+      } else {
+        dequant32<BIT>(load_raw<BIT>(idx_ptr(g, u, 0)), h_lo, lut0, lut1, my_lut4, step2);
+        dequant32<BIT>(load_raw<BIT>(idx_ptr(g, u, 1)), h_hi, lut0, lut1, my_lut4, step2);
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {   // k-step j covers this thread's codes 4j..4j+3
         const uint32_t af[4] = {h_lo[2 * j], h_hi[2 * j], h_lo[2 * j + 1], h_hi[2 * j + 1]};
@@ -244,20 +250,18 @@ __device__ void run_tile(const DecArgs& a, const DecPool& P, const TileCtx& tc, 
         for (int b = 0; b < 4; ++b) {
           if (b < tc.n_tb) {
             const uint2 bf = *reinterpret_cast<const uint2*>(xs + (8 * b + rl) * kXPitch + (32 * t4 + 4 * j) * 2);
-            mma_f16(acc[u][b], af, bf.x, bf.y);
+            mma_f16(acc[b], af, bf.x, bf.y);
           }
         }
       }
-    }
-#pragma unroll
-    for (int u = 0; u < 2; ++u)
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
-        total[u][b][0] = fmaf(acc[u][b][0], nrm[u][0], total[u][b][0]);
-        total[u][b][1] = fmaf(acc[u][b][1], nrm[u][0], total[u][b][1]);
-        total[u][b][2] = fmaf(acc[u][b][2], nrm[u][1], total[u][b][2]);
-        total[u][b][3] = fmaf(acc[u][b][3], nrm[u][1], total[u][b][3]);
+        total[u][b][0] = fmaf(acc[b][0], nrm[u][0], total[u][b][0]);
+        total[u][b][1] = fmaf(acc[b][1], nrm[u][0], total[u][b][1]);
+        total[u][b][2] = fmaf(acc[b][2], nrm[u][1], total[u][b][2]);
+        total[u][b][3] = fmaf(acc[b][3], nrm[u][1], total[u][b][3]);
       }
+    }
     __syncthreads();   // every thread is done with this buffer before group g+2 is staged into it
   }
 
@@ -283,7 +287,7 @@ __device__ void run_tile(const DecArgs& a, const DecPool& P, const TileCtx& tc, 
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) decode_mm_kernel(DecArgs a) {
+__global__ void __launch_bounds__(kThreads, 2) decode_mm_kernel(DecArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   uint8_t* s_x = smem;                                                        // 2 x 32 rows x kXPitch
   uint32_t* s_lut4 = reinterpret_cast<uint32_t*>(smem + 2 * kRowsMax * kXPitch);   // 16 entries x 32 lanes
@@ -346,6 +350,193 @@ int launch_decode(const dmoq_route_t* route, const dmoq_pool_t* pools, int n_poo
 }
 
 }  // namespace
+
+// ------------------------------------------------------------------------------------------------ rotations
+// Group rotations of the small-batch path, all pools in one launch.  WxA16 rotated activations are plain fp16
+// roundings of fp32-accumulated products (turboquant_utils/rotation.py:176; a floating-point stage, no code
+// exactness involved), so a small MMA block does it: 32 rows x 128 columns of one group per CTA, the rotation
+// matrix read from L2 as the col-major B operand (rot[j][k] is contiguous in k for output column j).
+//   gate_up side: rows of x (bf16 or fp16, cast to fp16 first as the reference does) -> every pool's table
+//                 (hoisted pools: one row per token; others: the pool's compact rows, sources in pool_src)
+//   down side:    rows of the SiLU output of every tile -> a_rot, with the rotation stack of the tile's expert
+struct RotPool {
+  const uint16_t* rot;     // gate_up: (G_h, 128, 128); down: (n_members * inter/128, 128, 128)
+  uint16_t* table;         // gate_up: destination table (rows, hidden)
+  int hoisted, cap_rows, inter;
+};
+struct RotDecArgs {
+  RotPool pool[DMOQ_MAX_POOLS];
+  int n_pools, is_down, hidden, T;
+  const void* x;           // gate_up: (T, hidden)
+  int x_is_bf16;
+  const int32_t* pool_rows;      // device: rows routed to each pool
+  const int32_t* pool_src;       // device: source token of each compact row
+  const int32_t* pool_src_base;  // device: first pool_src entry of each pool
+  const DmoqTile* tiles;
+  const int32_t* n_tiles;
+  const uint16_t* act;     // down: (R, act_stride) fp16
+  int act_stride;
+  uint16_t* a_rot;         // down: (R, a_stride) fp16
+  int a_stride;
+};
+
+__global__ void __launch_bounds__(128) decode_rotate_kernel(RotDecArgs a) {
+  __shared__ __align__(16) uint8_t s_x[kRowsMax * kXPitch];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, t4 = lane & 3, rl = lane >> 2;
+  int p, g = blockIdx.y, rows, src_kind;   // src_kind 0: x rows [row0, ..), 1: x rows through pool_src, 2: act rows
+  int row0 = 0, src_base = 0;
+  const uint16_t* rot;
+  uint16_t* dst;
+  int dst_pitch, dst_row0, dst_col0;
+  if (!a.is_down) {
+    p = blockIdx.z;
+    const RotPool& P = a.pool[p];
+    if (g >= a.hidden / kG) return;
+    const int n_rows = P.hoisted ? a.T : min(a.pool_rows[p], P.cap_rows);
+    row0 = blockIdx.x * kRowsMax;
+    if (row0 >= n_rows) return;
+    rows = min(kRowsMax, n_rows - row0);
+    src_kind = P.hoisted ? 0 : 1;
+    src_base = a.pool_src_base[p];
+    rot = P.rot + (size_t)g * kG * kG;
+    dst = P.table;
+    dst_pitch = a.hidden;
+    dst_row0 = row0;
+    dst_col0 = g * kG;
+  } else {
+    const int t = blockIdx.x;
+    p = -1;
+    for (int q = 0; q < a.n_pools; ++q) {
+      const int base = a.n_tiles[DMOQ_MAX_POOLS + q], n = a.n_tiles[q];
+      if (t >= base && t < base + n) p = q;
+    }
+    if (p < 0) return;
+    const RotPool& P = a.pool[p];
+    const int G = P.inter / kG;
+    if (g >= G) return;
+    const DmoqTile tile = a.tiles[t];
+    if (tile.rows <= 0) return;
+    rows = min(tile.rows, kRowsMax);
+    row0 = tile.row0;
+    src_kind = 2;
+    rot = P.rot + (size_t)(tile.rank * G + g) * kG * kG;
+    dst = a.a_rot;
+    dst_pitch = a.a_stride;
+    dst_row0 = row0;
+    dst_col0 = g * kG;
+  }
+  // ---- stage the rows' 128 values of this group as fp16
+  for (int c = tid; c < kRowsMax * 16; c += 128) {
+    const int r = c >> 4, ch = c & 15;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < rows) {
+      if (src_kind == 2) {
+        v = *reinterpret_cast<const uint4*>(a.act + (size_t)(row0 + r) * a.act_stride + g * kG + ch * 8);
+      } else {
+        const int src = src_kind == 0 ? row0 + r : a.pool_src[src_base + row0 + r];
+        v = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(a.x) + (size_t)src * a.hidden + g * kG + ch * 8);
+        if (a.x_is_bf16) {
+          uint16_t* u = reinterpret_cast<uint16_t*>(&v);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) u[q] = __half_as_ushort(__float2half_rn(bf16_bits_to_float(u[q])));
+        }
+      }
+    }
+    *reinterpret_cast<uint4*>(s_x + r * kXPitch + ch * 16) = v;
+  }
+  __syncthreads();
+  // ---- warp w: output columns [32w, 32w+32) for both 16-row tiles
+  float acc[2][4][4];
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[m][n][q] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    uint32_t af[2][4];
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+      const uint8_t* base = s_x + (16 * m + rl) * kXPitch + (16 * ks + 2 * t4) * 2;
+      af[m][0] = *reinterpret_cast<const uint32_t*>(base);
+      af[m][1] = *reinterpret_cast<const uint32_t*>(base + 8 * kXPitch);
+      af[m][2] = *reinterpret_cast<const uint32_t*>(base + 16);
+      af[m][3] = *reinterpret_cast<const uint32_t*>(base + 8 * kXPitch + 16);
+    }
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      const uint16_t* col = rot + (size_t)(32 * warp + 8 * n + rl) * kG + 16 * ks + 2 * t4;
+      const uint32_t b0 = *reinterpret_cast<const uint32_t*>(col), b1 = *reinterpret_cast<const uint32_t*>(col + 8);
+#pragma unroll
+      for (int m = 0; m < 2; ++m) mma_f16(acc[m][n], af[m], b0, b1);
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = 16 * m + rl + 8 * h;
+      if (r >= rows) continue;
+      uint16_t* orow = dst + (size_t)(dst_row0 + r) * dst_pitch + dst_col0 + 32 * warp + 2 * t4;
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        const __half2 v = __floats2half2_rn(acc[m][n][2 * h], acc[m][n][2 * h + 1]);
+        *reinterpret_cast<__half2*>(orow + 8 * n) = v;
+      }
+    }
+}
+
+extern "C" int dmoq_moe_decode_rotate(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t n_pools,
+                                      int32_t hidden, const void* x, int32_t x_is_bf16, void* stream) {
+  DMOQ_CHECK_ARG(route && pools_host && x && route->pool_rows && route->pool_src && route->pool_src_base);
+  DMOQ_CHECK_ARG(n_pools > 0 && n_pools <= DMOQ_MAX_POOLS && hidden > 0 && hidden % kG == 0 && route->T > 0);
+  RotDecArgs a{};
+  int max_rows = 0;
+  for (int i = 0; i < n_pools; ++i) {
+    const dmoq_pool_t& p = pools_host[i];
+    DMOQ_CHECK_ARG(p.mode == DMOQ_A16 && p.gu_rot && p.act_codes);
+    a.pool[i] = RotPool{p.gu_rot, static_cast<uint16_t*>(p.act_codes), p.hoisted, p.act_cap_rows, p.inter};
+    const int rows = p.hoisted ? route->T : p.act_cap_rows;
+    if (rows > max_rows) max_rows = rows;
+  }
+  a.n_pools = n_pools;
+  a.is_down = 0;
+  a.hidden = hidden;
+  a.T = route->T;
+  a.x = x;
+  a.x_is_bf16 = x_is_bf16;
+  a.pool_rows = route->pool_rows;
+  a.pool_src = route->pool_src;
+  a.pool_src_base = route->pool_src_base;
+  decode_rotate_kernel<<<dim3(dmoq_ceil_div(max_rows, kRowsMax), hidden / kG, n_pools), 128, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return dmoq_launch_status();
+}
+
+extern "C" int dmoq_moe_decode_rotate_down(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t n_pools,
+                                           const uint16_t* act, int32_t act_stride, uint16_t* a_rot, int32_t a_stride,
+                                           void* stream) {
+  DMOQ_CHECK_ARG(route && pools_host && act && a_rot && route->tiles && route->n_tiles && route->tile_m == kRowsMax);
+  DMOQ_CHECK_ARG(n_pools > 0 && n_pools <= DMOQ_MAX_POOLS && act_stride % 8 == 0 && a_stride % 8 == 0);
+  RotDecArgs a{};
+  int max_g = 0;
+  for (int i = 0; i < n_pools; ++i) {
+    const dmoq_pool_t& p = pools_host[i];
+    DMOQ_CHECK_ARG(p.mode == DMOQ_A16 && p.dn_rot && p.inter > 0 && p.inter % kG == 0);
+    a.pool[i] = RotPool{p.dn_rot, nullptr, 0, 0, p.inter};
+    if (p.inter / kG > max_g) max_g = p.inter / kG;
+  }
+  a.n_pools = n_pools;
+  a.is_down = 1;
+  a.tiles = reinterpret_cast<const DmoqTile*>(route->tiles);
+  a.n_tiles = route->n_tiles;
+  a.act = act;
+  a.act_stride = act_stride;
+  a.a_rot = a_rot;
+  a.a_stride = a_stride;
+  decode_rotate_kernel<<<dim3(route->tile_cap, max_g, 1), 128, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return dmoq_launch_status();
+}
 
 extern "C" int dmoq_moe_decode_gateup(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t n_pools,
                                       int32_t hidden, uint16_t* act, int32_t act_stride, void* stream) {

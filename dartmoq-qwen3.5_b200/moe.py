@@ -560,31 +560,34 @@ class _Engine:
             p.c.act_cap_rows = ws.caps[i]
             p.c.act_codes, p.c.act_scales = ws.act_codes[i].data_ptr(), ws.act_scales[i].data_ptr()
             self.pool_array[i] = p.c
+        if ws.decode:
+            # small batch (WxA16): five launches for all pools -- rotation, gate_up + SiLU, rotation, down, combine
+            n = len(self.pools)
+            check(lib.dmoq_moe_decode_rotate(C.byref(ws.route), self.pool_array, n, self.hidden, ptr(x), is_bf16, s),
+                  "dmoq_moe_decode_rotate")
+            mark("decode_rotate")
+            check(lib.dmoq_moe_decode_gateup(C.byref(ws.route), self.pool_array, n, self.hidden,
+                                             ptr(ws.act), self.inter_max, s), "dmoq_moe_decode_gateup")
+            mark("decode_gate_up_silu")
+            check(lib.dmoq_moe_decode_rotate_down(C.byref(ws.route), self.pool_array, n, ptr(ws.act), self.inter_max,
+                                                  ptr(ws.dn_codes), self.inter_max, s), "dmoq_moe_decode_rotate_down")
+            mark("decode_rotate_down")
+            check(lib.dmoq_moe_decode_down(C.byref(ws.route), self.pool_array, n, self.hidden,
+                                           ptr(ws.dn_codes), self.inter_max, ptr(ws.dn), s), "dmoq_moe_decode_down")
+            mark("decode_down")
+            self.last_launches = (1 if T * self.k_v <= 1024 and T <= 4096 else 3) + 5
+            y = torch.empty_like(x)
+            check(lib.dmoq_combine_weighted(C.byref(ws.route), ptr(ws.dn), self.hidden, ptr(y), is_bf16, s),
+                  "dmoq_combine_weighted")
+            mark("combine")
+            return y
+        for i, p in enumerate(self.pools):
             src_row = None if p.hoisted else C.c_void_p(ws.pool_src.data_ptr() + 4 * ws.pool_src_base_host[i])
             n_dev = None if p.hoisted else C.c_void_p(ws.pool_rows.data_ptr() + 4 * i)
             check(lib.dmoq_rotate_quant(p.mode, ptr(x), is_bf16, self.hidden, ptr(p.gu_rot), None, src_row,
                                         ws.caps[i], n_dev, p.c.gu_act_scale, ptr(ws.act_codes[i]),
                                         ptr(ws.act_scales[i]), s), "dmoq_rotate_quant")
         mark("rotate_quant")
-        if ws.decode:
-            # small batch: one streaming launch per projection for all pools
-            check(lib.dmoq_moe_decode_gateup(C.byref(ws.route), self.pool_array, len(self.pools), self.hidden,
-                                             ptr(ws.act), self.inter_max, s), "dmoq_moe_decode_gateup")
-            mark("decode_gate_up_silu")
-            for i, p in enumerate(self.pools):
-                check(lib.dmoq_rotate_quant_down(C.byref(ws.route), self.pool_array, i, ptr(ws.act), self.inter_max,
-                                                 ptr(ws.dn_codes), ptr(ws.dn_scales), self.inter_max, s),
-                      "dmoq_rotate_quant_down")
-            mark("rotate_quant_down")
-            check(lib.dmoq_moe_decode_down(C.byref(ws.route), self.pool_array, len(self.pools), self.hidden,
-                                           ptr(ws.dn_codes), self.inter_max, ptr(ws.dn), s), "dmoq_moe_decode_down")
-            mark("decode_down")
-            self.last_launches = (1 if T * self.k_v <= 1024 and T <= 4096 else 3) + 2 * len(self.pools) + 3
-            y = torch.empty_like(x)
-            check(lib.dmoq_combine_weighted(C.byref(ws.route), ptr(ws.dn), self.hidden, ptr(y), is_bf16, s),
-                  "dmoq_combine_weighted")
-            mark("combine")
-            return y
         img_modes = [self._image_mode(p, T, ws.tile_m) for p in self.pools]
         merged = (partials is None and len(self.pools) > 1 and all(m == 1 for m in img_modes)
                   and len({p.mode for p in self.pools}) == 1 and self.pools[0].mode != FP4)

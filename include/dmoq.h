@@ -296,6 +296,16 @@ int dmoq_widen_indices(const uint8_t* packed, int64_t n_bytes, int32_t bit, uint
  *           rows dn (R, hidden) for dmoq_combine_weighted
  * Pools must be A16 with bit 1, 2, 4, or 8 with the uniform codebook; hidden a multiple of 256.
  */
+/* The small-batch path's group rotations, all pools in one launch each (WxA16: rotated values are fp16 roundings of
+ * fp32-accumulated products, turboquant_utils/rotation.py:176 -- no activation codes involved):
+ *   rotate:      x (T, hidden) bf16/fp16 -> every pool's pool.act_codes table (hoisted pools: row = token; others:
+ *                the pool's compact rows through route->pool_src), rotation stack pool.gu_rot
+ *   rotate_down: act (R, act_stride) fp16 -> a_rot (R, a_stride) fp16, each tile with its expert's stack from
+ *                pool.dn_rot (quantization/wxa16/bit_partitioned_moe.py:934-943) */
+int dmoq_moe_decode_rotate(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t n_pools, int32_t hidden,
+                           const void* x, int32_t x_is_bf16, void* stream);
+int dmoq_moe_decode_rotate_down(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t n_pools,
+                                const uint16_t* act, int32_t act_stride, uint16_t* a_rot, int32_t a_stride, void* stream);
 int dmoq_moe_decode_gateup(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t n_pools, int32_t hidden,
                            uint16_t* act, int32_t act_stride, void* stream);
 int dmoq_moe_decode_down(const dmoq_route_t* route, const dmoq_pool_t* pools_host, int32_t n_pools, int32_t hidden,
