@@ -34,6 +34,8 @@ __device__ unsigned long long g_img_prof[32];
 #define PROF_DECL long long prof_t0 = 0, prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
 #define PROF_BEGIN() prof_t0 = clock64()
 #define PROF_END(i) prof_acc[i] += clock64() - prof_t0
+#define PROF_BEGIN2() const long long prof_t1 = clock64()
+#define PROF_END2(i) prof_acc[i] += clock64() - prof_t1
 #define PROF_FLUSH(base, cond)                                                        \
   if ((cond) && blockIdx.x == 0 && lane == 0) {                                       \
     for (int i_ = 0; i_ < 8; ++i_) atomicAdd(&g_img_prof[(base) + i_], (unsigned long long)prof_acc[i_]); \
@@ -42,6 +44,8 @@ __device__ unsigned long long g_img_prof[32];
 #define PROF_DECL
 #define PROF_BEGIN()
 #define PROF_END(i)
+#define PROF_BEGIN2()
+#define PROF_END2(i)
 #define PROF_FLUSH(base, cond)
 #endif
 
@@ -114,55 +118,73 @@ struct ImgArgs {
 };
 
 // ------------------------------------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+// Every shared-memory operand below is an address in the shared window (32 bits): the kernel derives them all from
+// one base it computed once, so no loop recomputes a pointer.
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t parity, uint32_t ns) {
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "r"(bar), "r"(parity), "r"(ns)
       : "memory");
   return ok != 0;
 }
 // Bounded wait (about one second).  Returns false, and raises the abort flag, if the phase never completes; once
 // the flag is up every later wait returns at once.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ int abort_get(uint32_t flag) {
+  int v;
+  asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(flag) : "memory");
+  return v;
+}
+__device__ __forceinline__ void abort_set(uint32_t flag) {
+  asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(flag), "r"(1) : "memory");
+}
+// Bounded wait (about one second).  Returns false, and raises the abort flag, if the phase never completes; once
+// the flag is up every later wait returns at once.  A waiting warp shares its scheduler with epilogue warps: it
+// probes, sleeps a little where its role can afford the latency, and looks at the abort flag and the clock only
+// every 32nd probe.
+template <int SLEEP_NS = 0>
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  if (*abort_flag) return false;
+  if (abort_get(abort_flag)) return false;
   const long long t0 = clock64();
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
     if (mbar_try_wait_suspend(bar, parity, 100000u)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) break;
+    if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
+    if ((spin & 31u) == 31u) {
+      if (abort_get(abort_flag)) return false;
+      if (clock64() - t0 > kWaitCycles) break;
+    }
   }
-  *abort_flag = 1;
+  abort_set(abort_flag);
   atomicOr(&g_dmoq_img_status, 1);
   return false;
 }
 // Time-bounded wait that ignores the abort flag: used at teardown so that no bulk copy is still writing into this
 // block's shared memory when it exits.
-__device__ __forceinline__ void mbar_wait_quiet(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ void mbar_wait_quiet(uint32_t bar, uint32_t parity) {
   const long long t0 = clock64();
   while (!mbar_try_wait_suspend(bar, parity, 100000u)) {
     if (clock64() - t0 > kWaitCycles) break;
@@ -170,23 +192,22 @@ __device__ __forceinline__ void mbar_wait_quiet(uint64_t* bar, uint32_t parity) 
 }
 // 2-D tile of a tensor map -> this block's shared memory; completion counted in bytes on the barrier.  The map lies
 // over this GPU's own memory; the inner coordinate x is a multiple of 16 bytes.
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
-__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+__device__ __forceinline__ void bulk_g2s(uint32_t smem_dst, const void* gmem_src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               ::"r"(smem_dst), "l"(gmem_src), "r"(bytes), "r"(bar)
                : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 template <int MODE>
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -238,7 +259,50 @@ __device__ __forceinline__ void tc_st4(uint32_t taddr, uint32_t v0, uint32_t v1,
   asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(v0), "r"(v1), "r"(v2), "r"(v3)
                : "memory");
 }
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+// 16 lanes x 16 columns: thread t = 4*i + q of the warp receives lane base+i (r0,r1,r4,r5) and lane base+i+8
+// (r2,r3,r6,r7) at columns 2q, 2q+1 (r0..r3) and 8+2q, 9+2q (r4..r7); the lane base is the warp's quarter or 16 above it
+__device__ __forceinline__ void tc_ld16x16(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+// 16 lanes x 16 columns of one value (the block of one tc_ld16x16).  A store takes its values from consecutive
+// registers, so two stores of four keep four registers busy with the constant instead of eight.
+__device__ __forceinline__ void tc_st16x16_fill(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1,%1,%1,%1};" ::"r"(taddr), "r"(v) : "memory");
+  asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1,%1,%1,%1};" ::"r"(taddr + 8), "r"(v) : "memory");
+}
+// Pairs of fp32 values live in 64-bit registers from the load to the last fused multiply-add, so that no
+// pack / unpack moves stand between the packed instructions.
+typedef unsigned long long f32x2_t;
+__device__ __forceinline__ f32x2_t lds_x2(uint32_t addr) {
+  f32x2_t v;
+  asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ f32x2_t pack_x2(uint32_t lo, uint32_t hi) {
+  f32x2_t v;
+  asm("mov.b64 %0, {%1,%2};" : "=l"(v) : "r"(lo), "r"(hi));
+  return v;
+}
+// the same, kept in program order with the other volatile statements: for registers an asynchronous TMEM load
+// fills, which must not be read before the tcgen05.wait::ld that precedes this statement
+__device__ __forceinline__ f32x2_t pack_x2_after_wait(uint32_t lo, uint32_t hi) {
+  f32x2_t v;
+  asm volatile("mov.b64 %0, {%1,%2};" : "=l"(v) : "r"(lo), "r"(hi));
+  return v;
+}
+__device__ __forceinline__ float2 unpack_x2(f32x2_t v) {
+  float2 f;
+  asm("mov.b64 {%0,%1}, %2;" : "=f"(f.x), "=f"(f.y) : "l"(v));
+  return f;
+}
+__device__ __forceinline__ f32x2_t fma_x2(f32x2_t a, f32x2_t b, f32x2_t c) {
+  f32x2_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
 
 // K-major, 128-byte swizzle: tile row r is 128 bytes; 16-byte chunk c lives at slot c ^ (r & 7); groups of 8 rows
 // are 1024 bytes apart (the descriptor's stride byte offset).  The TMA copy writes the same pattern.
@@ -278,24 +342,36 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   Smem<BN>& S = *reinterpret_cast<Smem<BN>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  volatile int* abort_flag = &S.abort_flag;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // a broadcast value: the compiler keeps what derives from it in uniform registers
+  // one base address in the shared window, opaque to the optimiser (it would otherwise recompute the aligned base
+  // at every use); every tile, norm slot and barrier is a compile-time offset from it
+  uint32_t sb = smem_u32(&S);
+  asm volatile("" : "+r"(sb));
+  using SM = Smem<BN>;
+  const uint32_t abort_flag = sb + (uint32_t)offsetof(SM, abort_flag);
+  auto bar_full = [&](uint32_t s_) { return sb + (uint32_t)offsetof(SM, full) + 8u * s_; };
+  auto bar_empty = [&](uint32_t s_) { return sb + (uint32_t)offsetof(SM, empty) + 8u * s_; };
+  auto bar_acc_full = [&](uint32_t b_) { return sb + (uint32_t)offsetof(SM, acc_full) + 8u * b_; };
+  auto bar_acc_empty = [&](uint32_t b_) { return sb + (uint32_t)offsetof(SM, acc_empty) + 8u * b_; };
+  auto tile_a = [&](uint32_t s_) { return sb + (uint32_t)offsetof(SM, a) + (uint32_t)kTileA * s_; };
+  auto tile_b = [&](uint32_t s_) { return sb + (uint32_t)offsetof(SM, b) + (uint32_t)C::kTileB * s_; };
+  auto norm_slot = [&](uint32_t i_) { return sb + (uint32_t)offsetof(SM, norm) + (uint32_t)(BN * 4) * i_; };
   constexpr int SPG = Shape<MODE>::SPG, GPS = Shape<MODE>::GPS;
   constexpr int ACC = (BN == 256) ? 2 : (MODE == DMOQ_FP4 ? 3 : 4);   // accumulator buffers in TMEM
   constexpr int NH = BN / 128;                                        // 32-column blocks per epilogue thread
-  constexpr int CW = 8;                                               // accumulator columns per TMEM load
-  constexpr int NCH = 32 * NH / CW;                                   // loads per group and thread (even)
+  constexpr int NCH = 4 * NH;                                         // 16-lane x 16-column accumulator loads per group and warp
   constexpr int kMmaWarp = C::kMmaWarp, kNormRing = C::kNormRing;
   static_assert(!(MODE == DMOQ_FP4 && BN != 128), "the FP4 scale-factor columns need 128-column tiles");
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&S.full[s], MODE == DMOQ_FP4 ? 5 : 1);   // the thread that announces the bulk bytes (+ four scale warps)
-      mbar_init(&S.empty[s], 1);
+      mbar_init(bar_full(s), MODE == DMOQ_FP4 ? 5 : 1);   // the thread that announces the bulk bytes (+ four scale warps)
+      mbar_init(bar_empty(s), 1);
     }
     for (int b = 0; b < 4; ++b) {
-      mbar_init(&S.acc_full[b], 1);
-      mbar_init(&S.acc_empty[b], kEpiWarps);
+      mbar_init(bar_acc_full(b), 1);
+      mbar_init(bar_acc_empty(b), kEpiWarps);
     }
     S.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -307,7 +383,7 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = S.tmem_base;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, S.tmem_base, 0);
   if (MODE == DMOQ_A8 || MODE == DMOQ_FP4) {
     if (warp < kEpiWarps) {
       const uint32_t t0 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
@@ -375,39 +451,44 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
 
   if (warp < kEpiWarps) {
     // =========================================================================== epilogue warps
+    // Accumulators come out of TMEM in the 16x256b shape: of a block of 16 lanes x 16 columns thread t = 4*i + q
+    // receives rows i and i + 8 at columns 2q, 2q+1, 8+2q, 9+2q.  A thread therefore owns FOUR rows (i, i+8, i+16,
+    // i+24 of its warp's lane quarter) and 16*NH of the warp's 32*NH columns, needs only 16*NH column norms per
+    // group (64-bit shared loads with four distinct addresses per warp) and four row scales.
     reg_inc<C::kRegsEpi>();
     const int lq = warp & 3, cq = warp >> 2;
-    const int row = lq * 32 + lane;                  // tile row of this thread
-    const int cbase = cq * (32 * NH);                // first of this thread's 32*NH tile columns
-    const uint32_t t_lane = tmem_base + ((uint32_t)(lq * 32) << 16) + cbase;
+    const int li = lane >> 2, qd = lane & 3;
+    const int cbase = cq * (32 * NH);                // first of the warp's 32*NH tile columns
+    uint32_t t_acc = tmem_base + ((uint32_t)(lq * 32) << 16) + cbase;     // the warp's corner of accumulator 0
+    uint32_t norm_u32 = norm_slot(0) + (uint32_t)(cbase + 2 * qd) * 4u;     // this thread's first norm pair of slot 0
+    asm volatile("" : "+r"(t_acc), "+r"(norm_u32));                        // kept in registers, not recomputed per use
     const int xs_per_row = a.a_stride / kG;
+    const unsigned short* xs_tab = reinterpret_cast<const unsigned short*>(a.a_scales);
+    constexpr bool has_xs = (MODE == DMOQ_A8 || MODE == DMOQ_FP8);
     uint32_t ia = 0;                                 // groups consumed so far
     uint32_t v[2][8];                                // accumulator chunks: one in the scale math, one in flight
-    bool prefetched = false;                         // the upcoming group's first chunk is already on its way
-    Item next = item_of(0);
     PROF_DECL;
 #ifdef DMOQ_IMG_PROFILE
     const long long prof_start = clock64();
 #endif
     for (int item = 0; item < n_items; ++item) {
-      const Item cur = next;
-      next = item_of(item + 1);
+      const Item cur = item_of(item);
       const DmoqTile tile = cur.tile;
       const int nb = cur.nb, G = cur.G, inter = a.pp[cur.q].inter;
-      const bool live = row < tile.rows;
-      // row scales: this row's G fp16 values, fetched four at a time (8-byte loads, one block ahead) where the row
-      // pitch allows, else one at a time
-      const bool has_xs = (MODE == DMOQ_A8 || MODE == DMOQ_FP8);
-      const __half* xs_row = reinterpret_cast<const __half*>(a.a_scales) + (size_t)(tile.row0 + (live ? row : 0)) * xs_per_row;
-      const bool xs_vec = (xs_per_row & 3) == 0;
-      float2 total2[16 * NH];   // pair p = this thread's columns 2p, 2p+1
+      // thread row r = 2*h + j: tile row lq*32 + 16*h + 8*j + li
+      int xoff[4];                                   // element offset of the row's scales (row 0 of the tile for rows past its end)
 #pragma unroll
-      for (int c = 0; c < 16 * NH; ++c) total2[c] = make_float2(0.f, 0.f);
-      uint2 xq = make_uint2(0u, 0u), xq_next = make_uint2(0u, 0u);
-      float xs_next = 0.f;
+      for (int r = 0; r < 4; ++r) {
+        const int row = lq * 32 + 8 * r + li;
+        xoff[r] = (tile.row0 + (row < tile.rows ? row : 0)) * xs_per_row;
+      }
+      f32x2_t total2[NCH * 4];   // [chunk c = 2k + h][pair p = j + 2m]: columns 16k + 8m + 2q, +1 of row 2h + j
+#pragma unroll
+      for (int c = 0; c < NCH * 4; ++c) total2[c] = 0ull;
+      uint32_t xraw[4] = {0u, 0u, 0u, 0u};           // the upcoming group's row scales (fp16 bits), one group ahead
       if (has_xs) {
-        if (xs_vec) xq_next = *reinterpret_cast<const uint2*>(xs_row);
-        else xs_next = __half2float(xs_row[0]);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) xraw[r] = xs_tab[xoff[r]];
       }
       int held = -1;     // accumulator buffer whose release is still owed (its bias stores are in flight)
       auto release = [&]() {
@@ -415,85 +496,80 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
           if (MODE == DMOQ_A8) tc_wait_st();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&S.acc_empty[held]);
+          if (lane == 0) mbar_arrive(bar_acc_empty((uint32_t)held));
           held = -1;
         }
       };
 
       for (int g = 0; g < G; ++g, ++ia) {
         const uint32_t b = ia % ACC, ph = (ia / ACC) & 1;
-        const uint32_t slot = ia % kNormRing;
-        float xs = 0.f;
+        const uint32_t nrm = norm_u32 + (ia % kNormRing) * (uint32_t)(BN * 4);
+        f32x2_t xs2[4], off2[4];
         if (has_xs) {
-          if (xs_vec) {
-            if ((g & 3) == 0) {
-              xq = xq_next;
-              if (g + 4 < G) xq_next = *reinterpret_cast<const uint2*>(xs_row + g + 4);   // in flight during these groups
-            }
-            const uint32_t w = (g & 2) ? xq.y : xq.x;
-            xs = __half2float(__ushort_as_half((unsigned short)((g & 1) ? (w >> 16) : (w & 0xFFFFu))));
-          } else {
-            xs = xs_next;
-            if (g + 1 < G) xs_next = __half2float(xs_row[g + 1]);
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const float x = __half2float(__ushort_as_half((unsigned short)xraw[r]));
+            xs2[r] = pack_x2(__float_as_uint(x), __float_as_uint(x));
+            // INT8: (acc_biased - M) * xs in one fma with the exact constant -M*xs; e4m3: acc * xs
+            const float o = (MODE == DMOQ_A8) ? -kMagicFloat * x : 0.f;
+            off2[r] = pack_x2(__float_as_uint(o), __float_as_uint(o));
+          }
+          if (g + 1 < G) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) xraw[r] = xs_tab[xoff[r] + g + 1];   // in flight during this group
           }
         }
         // The group's norms were bulk-copied before its operand stage completed; the MMA thread saw that completion
         // before it committed acc_full[], so they are visible here.
-        if (!prefetched) {
-          PROF_BEGIN();
-          mbar_wait(&S.acc_full[b], ph, abort_flag);   // on a timeout the flag is up and the data is void
-          PROF_END(0);
-          tc_fence_after();
-          tc_ld8(t_lane + b * BN, v[0]);
-        }
-        prefetched = false;
         PROF_BEGIN();
-        const float2 xs2 = make_float2(xs, xs);
-        const float off = (MODE == DMOQ_A8) ? -kMagicFloat * xs : 0.f;
-        const float2 off2 = make_float2(off, off);
-        // The thread's 32*NH columns in chunks of eight: the load of chunk c+1 (at the end of a group: of the next
-        // group's first chunk, if that group is ready) is in flight while chunk c goes through the scale math.
+        mbar_wait(bar_acc_full(b), ph, abort_flag);   // on a timeout the flag is up and the data is void
+        PROF_END(0);
+        tc_fence_after();
+        tc_ld16x16(t_acc + b * BN, v[0]);
+        PROF_BEGIN();
+        // Chunks of 16 lanes x 16 columns, c = 2k + h (column block k, lane half h): the load of chunk c+1 is in
+        // flight while chunk c goes through the scale math.  The two lane halves of a column block share its norms.
+        f32x2_t nr[2];
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
-          tc_wait_ld();
+          const int k = c >> 1, h = c & 1;
+          if (h == 0) {
+            nr[0] = lds_x2(nrm + (uint32_t)(k * 64));
+            nr[1] = lds_x2(nrm + (uint32_t)(k * 64 + 32));
+          }
+          {
+            PROF_BEGIN2();
+            tc_wait_ld();
+            PROF_END2(1);   // a part of the chunk loop's time
+          }
           // the previous group's buffer goes back to the MMA thread here: its bias stores were issued a whole group
           // ago, so waiting for them costs nothing now
           if (c == 0) release();
-          if (c + 1 < NCH) {
-            tc_ld8(t_lane + b * BN + CW * (c + 1), v[(c + 1) & 1]);
-          } else if (g + 1 < G || item + 1 < n_items) {
-            const uint32_t bn_ = (ia + 1) % ACC, phn = ((ia + 1) / ACC) & 1;
-            if (mbar_try_wait(&S.acc_full[bn_], phn)) {
-              tc_fence_after();
-              tc_ld8(t_lane + bn_ * BN, v[(c + 1) & 1]);
-              prefetched = true;
-            }
-          }
-          if (MODE == DMOQ_A8) tc_st8_fill(t_lane + b * BN + CW * c, kMagicBits);   // re-arm the bias for the buffer's next use
+          const uint32_t t_chunk = t_acc + ((c & 1) ? (16u << 16) : 0u) + b * BN + 16 * (c >> 1);
+          if (MODE == DMOQ_A8) tc_st16x16_fill(t_chunk, kMagicBits);   // the chunk has landed: re-arm the bias for the buffer's next use
+          if (c + 1 < NCH) tc_ld16x16(t_acc + (((c + 1) & 1) ? (16u << 16) : 0u) + b * BN + 16 * ((c + 1) >> 1), v[(c + 1) & 1]);
           const uint32_t(&vc)[8] = v[c & 1];
-          const float4* nrm4 = reinterpret_cast<const float4*>(&S.norm[slot][cbase + CW * c]);
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            const float4 n4 = nrm4[q];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int j = 4 * q + 2 * e;
-              const float2 f = make_float2(__uint_as_float(vc[j]), __uint_as_float(vc[j + 1]));
-              const float2 n2 = e ? make_float2(n4.z, n4.w) : make_float2(n4.x, n4.y);
-              // INT8: (acc_biased - M) * xs in one fma with the exact constant -M*xs; e4m3: acc * xs;
-              // fp16 / e2m1 operands: no row scale (the block scales are applied by the MMA)
-              const float2 t2 = (MODE == DMOQ_A8 || MODE == DMOQ_FP8) ? fma2(f, xs2, off2) : f;
-              total2[(CW * c + j) >> 1] = fma2(t2, n2, total2[(CW * c + j) >> 1]);
-            }
+          for (int p = 0; p < 4; ++p) {   // p = j + 2m
+            const int r = 2 * h + (p & 1);
+            const f32x2_t f = pack_x2_after_wait(vc[2 * p], vc[2 * p + 1]);
+            // fp16 / e2m1 operands: no row scale (the block scales are applied by the MMA)
+            const f32x2_t t2 = has_xs ? fma_x2(f, xs2[r], off2[r]) : f;
+            total2[c * 4 + p] = fma_x2(t2, nr[p >> 1], total2[c * 4 + p]);
           }
-          if (BN == 128 && MODE == DMOQ_A8 && a.partials != nullptr && live) {   // parity checks only (128-column tiles)
+          if (BN == 128 && MODE == DMOQ_A8 && a.partials != nullptr) {   // parity checks only (128-column tiles)
             const int n_out = a.is_down ? a.hidden : 2 * inter;
 #pragma unroll
-            for (int j = 0; j < CW; ++j) {
-              const int col = CW * c + j;                                        // 0..31
-              const int n = a.is_down ? nb * BN + cbase + col
-                                      : (col < 16 ? 0 : inter) + nb * (BN / 2) + cq * 16 + (col & 15);
-              a.partials[((size_t)(tile.row0 + row) * n_out + n) * G + g] = (int32_t)(vc[j] - kMagicBits);
+            for (int p = 0; p < 4; ++p) {
+              const int row = lq * 32 + 16 * h + 8 * (p & 1) + li;
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int col = 16 * k + 8 * (p >> 1) + 2 * qd + e;              // 0..31 within the warp's block
+                const int n = a.is_down ? nb * BN + cbase + col
+                                        : (col < 16 ? 0 : inter) + nb * (BN / 2) + cq * 16 + (col & 15);
+                if (row < tile.rows)
+                  a.partials[((size_t)(tile.row0 + row) * n_out + n) * G + g] = (int32_t)(vc[2 * p + e] - kMagicBits);
+              }
             }
           }
         }
@@ -503,62 +579,75 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
       release();   // before the tile's output stores: the MMA thread may run ahead into the next item
       PROF_BEGIN();
 
-      // ---- tile epilogue: a thread owns 32*NH consecutive image columns of its row
+      // ---- tile epilogue: a thread stores pairs of adjacent columns (4 bytes); the four threads of a quad fill 16
+      // contiguous bytes of a row, the next pair of the same threads the 16 bytes after them.  One pointer per row,
+      // at the thread's first column of the item; every store is that pointer plus a compile-time offset.
+      uint16_t* rowp[4];
+      bool live[4];
+      {
+        const int col0 = (EPI != DMOQ_EPI_SILU && a.is_down) ? nb * BN + cbase + 2 * qd : nb * (BN / 2) + cq * NH * 16 + 2 * qd;
 #pragma unroll
-      for (int h = 0; h < NH; ++h) {
-        if (EPI == DMOQ_EPI_SILU) {   // image columns [0,16) of the block = gate, [16,32) = up of 16 consecutive outputs
-          uint32_t pk[8];
+        for (int r = 0; r < 4; ++r) {
+          const int row = lq * 32 + 8 * r + li;
+          live[r] = row < tile.rows;
+          rowp[r] = reinterpret_cast<uint16_t*>(a.out) + (size_t)(tile.row0 + row) * a.out_stride + col0;
+        }
+      }
+      if (EPI == DMOQ_EPI_SILU) {
+        // image columns [0,16) of a 32-column block = gate, [16,32) = up of 16 consecutive outputs: chunks 2*h2 and
+        // 2*h2 + 1 hold a thread's gate and up values at the same positions
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float o[2];
+        for (int h2 = 0; h2 < NH; ++h2)
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const float gate = __half2float(__float2half_rn(e ? total2[16 * h + j].y : total2[16 * h + j].x));
-              const float up = __half2float(__float2half_rn(e ? total2[16 * h + 8 + j].y : total2[16 * h + 8 + j].x));
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+              const float2 gt = unpack_x2(total2[(4 * h2 + h) * 4 + p]), ut = unpack_x2(total2[(4 * h2 + 2 + h) * 4 + p]);
+              const __half2 uh = __floats2half2_rn(ut.x, ut.y);                       // fp16 up
+              const float2 gf = __half22float2(__floats2half2_rn(gt.x, gt.y));        // fp16 gate, back in fp32
               // fast exp and reciprocal (a few fp32 ulps) ahead of the fp16 rounding: a floating-point stage
-              const float sg = __half2float(__float2half_rn(__fdividef(gate, 1.0f + __expf(-gate))));
-              o[e] = __fmul_rn(sg, up);
+              const __half2 sg = __floats2half2_rn(__fdividef(gf.x, 1.0f + __expf(-gf.x)), __fdividef(gf.y, 1.0f + __expf(-gf.y)));
+              // fp16(silu * up): the product of two fp16 values is exact in fp32, so one fp16 multiply rounds the same
+              const __half2 o2 = __hmul2(sg, uh);
+              const int r = 2 * h + (p & 1);
+              if (live[r]) *reinterpret_cast<uint32_t*>(rowp[r] + h2 * 16 + 8 * (p >> 1)) = *reinterpret_cast<const uint32_t*>(&o2);
             }
-            const __half2 h2 = __floats2half2_rn(o[0], o[1]);
-            pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
-          }
-          if (live) {
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.out) + (size_t)(tile.row0 + row) * a.out_stride +
-                                                  nb * (BN / 2) + (cq * NH + h) * 16);
-            dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-          }
-        } else {
-          float wgt = 0.f;
-          if (EPI == DMOQ_EPI_WEIGHTED && live) wgt = a.row_weight[tile.row0 + row];
-          uint32_t pk[16];
+      } else {
+        float wgt[4] = {0.f, 0.f, 0.f, 0.f};
+        if (EPI == DMOQ_EPI_WEIGHTED) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const __half2 h2 = __floats2half2_rn(total2[16 * h + j].x, total2[16 * h + j].y);   // the fp16 output
-            if (EPI == DMOQ_EPI_WEIGHTED) {   // -> bf16, times the routing weight in fp32, -> bf16
-              const float2 hf = __half22float2(h2);
-              const float2 bf = __bfloat1622float2(__floats2bfloat162_rn(hf.x, hf.y));
-              const __nv_bfloat162 o2 = __floats2bfloat162_rn(__fmul_rn(bf.x, wgt), __fmul_rn(bf.y, wgt));
-              pk[j] = *reinterpret_cast<const uint32_t*>(&o2);
-            } else {
-              pk[j] = *reinterpret_cast<const uint32_t*>(&h2);
-            }
+          for (int r = 0; r < 4; ++r)
+            if (live[r]) wgt[r] = a.row_weight[tile.row0 + lq * 32 + 8 * r + li];
+        }
+        auto out_bits = [&](int c, int p) {
+          const float2 tv = unpack_x2(total2[c * 4 + p]);
+          const __half2 hv = __floats2half2_rn(tv.x, tv.y);   // the fp16 output
+          uint32_t bits = *reinterpret_cast<const uint32_t*>(&hv);
+          if (EPI == DMOQ_EPI_WEIGHTED) {   // -> bf16, times the routing weight in fp32, -> bf16
+            const float w = wgt[2 * (c & 1) + (p & 1)];
+            const float2 hf = __half22float2(hv);
+            const float2 bf = __bfloat1622float2(__floats2bfloat162_rn(hf.x, hf.y));
+            const __nv_bfloat162 o2 = __floats2bfloat162_rn(__fmul_rn(bf.x, w), __fmul_rn(bf.y, w));
+            bits = *reinterpret_cast<const uint32_t*>(&o2);
           }
-          if (live) {
-            uint16_t* orow = reinterpret_cast<uint16_t*>(a.out) + (size_t)(tile.row0 + row) * a.out_stride;
-            if (a.is_down) {
-              uint4* dst = reinterpret_cast<uint4*>(orow + nb * BN + cbase + 32 * h);
+          return bits;
+        };
+        if (a.is_down) {   // tile columns are output columns
 #pragma unroll
-              for (int q = 0; q < 4; ++q) dst[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-            } else {   // plain gate_up rows: [gate | up], each inter wide
-              uint4* dg = reinterpret_cast<uint4*>(orow + nb * (BN / 2) + (cq * NH + h) * 16);
-              uint4* du = reinterpret_cast<uint4*>(orow + inter + nb * (BN / 2) + (cq * NH + h) * 16);
-              dg[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-              dg[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-              du[0] = make_uint4(pk[8], pk[9], pk[10], pk[11]);
-              du[1] = make_uint4(pk[12], pk[13], pk[14], pk[15]);
+          for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+              const int r = 2 * (c & 1) + (p & 1);
+              if (live[r]) *reinterpret_cast<uint32_t*>(rowp[r] + 16 * (c >> 1) + 8 * (p >> 1)) = out_bits(c, p);
             }
-          }
+        } else {           // plain gate_up rows are [gate | up], each inter wide
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+              const int k = c >> 1, r = 2 * (c & 1) + (p & 1);
+              if (live[r]) *reinterpret_cast<uint32_t*>(rowp[r] + ((k & 1) ? inter : 0) + (k >> 1) * 16 + 8 * (p >> 1)) = out_bits(c, p);
+            }
         }
       }
       PROF_END(4);
@@ -593,16 +682,16 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
         for (int st = 0; st < steps_per_item; ++st, ++it) {
           const int s = it % kStages;
           PROF_BEGIN();
-          mbar_wait(&S.empty[s], ((it / kStages) & 1) ^ 1, abort_flag);
+          mbar_wait<200>(bar_empty(s), ((it / kStages) & 1) ^ 1, abort_flag);
           PROF_END(0);
           PROF_BEGIN();
           if (loader) {
-            if (!*abort_flag) {
+            if (!abort_get(abort_flag)) {
               // A tile: rows [row0, +128) of the sorted code table, 128 bytes of the step; B tile: image rows
               // [img_row0, +BN) of the step's image row group; column norms of the groups the step starts
               const int g_first = (st * GPS) / SPG;
               const int n_groups = (SPG == 2) ? ((st & 1) ? 0 : 1) : min(GPS, G - g_first);
-              mbar_arrive_expect_tx(&S.full[s], kTileA + C::kTileB + n_groups * BN * 4);
+              mbar_arrive_expect_tx(bar_full(s), kTileA + C::kTileB + n_groups * BN * 4);
               int x, y;
               if (MODE == DMOQ_A16) {
                 x = (st & 1) * 128;
@@ -614,12 +703,12 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
                 x = 0;
                 y = (gg0 + st) * pp.n_img + img_row0;
               }
-              tma_load_2d(&S.a[s][0], &maps.a, st * 128, tile.row0, &S.full[s]);
-              tma_load_2d(&S.b[s][0], &maps.b[cur.q], x, y, &S.full[s]);
+              tma_load_2d(tile_a(s), &maps.a, st * 128, tile.row0, bar_full(s));
+              tma_load_2d(tile_b(s), &maps.b[cur.q], x, y, bar_full(s));
               for (int j = 0; j < n_groups; ++j, ++ig)
-                bulk_g2s(&S.norm[ig % kNormRing][0], pp.norm_img + (size_t)(gg0 + g_first + j) * pp.n_img + img_row0, BN * 4, &S.full[s]);
+                bulk_g2s(norm_slot(ig % kNormRing), pp.norm_img + (size_t)(gg0 + g_first + j) * pp.n_img + img_row0, BN * 4, bar_full(s));
             } else {
-              mbar_arrive(&S.full[s]);   // keep the arrival count whole after an abort
+              mbar_arrive(bar_full(s));   // keep the arrival count whole after an abort
             }
           }
           PROF_END(1);
@@ -640,7 +729,7 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
             tc_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&S.full[s]);
+            if (lane == 0) mbar_arrive(bar_full(s));
             PROF_END(2);
           }
         }
@@ -651,7 +740,7 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
       PROF_FLUSH(8, warp == kEpiWarps);
       // no bulk copy may still be in flight when the block exits (matters after an abort)
       if (loader)
-        for (uint32_t j = (it > (uint32_t)kStages ? it - kStages : 0u); j < it; ++j) mbar_wait_quiet(&S.full[j % kStages], (j / kStages) & 1);
+        for (uint32_t j = (it > (uint32_t)kStages ? it - kStages : 0u); j < it; ++j) mbar_wait_quiet(bar_full(j % kStages), (j / kStages) & 1);
     } else if (warp == kMmaWarp) {
       // ========================================================================= MMA warp
       constexpr uint32_t nm = ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
@@ -671,7 +760,7 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
         for (int st = 0; st < steps_per_item; ++st, ++it) {
           const int s = it % kStages;
           PROF_BEGIN();
-          bool ok = mbar_wait(&S.full[s], (it / kStages) & 1, abort_flag);
+          bool ok = mbar_wait<40>(bar_full(s), (it / kStages) & 1, abort_flag);
           PROF_END(0);
           PROF_BEGIN();
           const int n_groups = (SPG == 2) ? 1 : min(GPS, G - st * GPS);
@@ -679,15 +768,15 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
           if (SPG == 1 || (st & 1) == 0) {
             for (int j = 0; j < n_groups; ++j) {
               const uint32_t ib = ia + j;
-              ok = mbar_wait(&S.acc_empty[ib % ACC], ((ib / ACC) & 1) ^ 1, abort_flag) && ok;
+              ok = mbar_wait<40>(bar_acc_empty(ib % ACC), ((ib / ACC) & 1) ^ 1, abort_flag) && ok;
             }
           }
           PROF_END(1);
           PROF_BEGIN();
           tc_fence_after();
           if (lane == 0 && ok) {
-            const uint64_t da = make_desc(smem_u32(&S.a[s][0]));
-            const uint64_t db = make_desc(smem_u32(&S.b[s][0]));
+            const uint64_t da = make_desc(tile_a(s));
+            const uint64_t db = make_desc(tile_b(s));
             if (MODE == DMOQ_FP4) {
               for (int j = 0; j < n_groups; ++j) {
                 const uint32_t b = (ia + j) % ACC;
@@ -697,9 +786,9 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
                   const uint32_t idesc = idesc_f4 | ((uint32_t)(2 * k) << 4) | ((uint32_t)(2 * k) << 29);
                   tc_mma_mxf4(tmem_base + b * BN, da + 2 * (2 * j + k), db + 2 * (2 * j + k), idesc, sfa, tmem_base + kSfbCol, k > 0);
                 }
-                tc_commit(&S.acc_full[b]);
+                tc_commit(bar_acc_full(b));
               }
-              tc_commit(&S.empty[s]);
+              tc_commit(bar_empty(s));
             } else {
               const uint32_t b = ia % ACC;
               const uint32_t d = tmem_base + b * BN;
@@ -709,8 +798,8 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
                 else if (MODE == DMOQ_FP8) tc_mma<DMOQ_FP8>(d, da + 2 * k, db + 2 * k, idesc_f8, k > 0);
                 else tc_mma<DMOQ_A16>(d, da + 2 * k, db + 2 * k, idesc_f16, ((st & 1) || k > 0) ? 1u : 0u);
               }
-              tc_commit(&S.empty[s]);
-              if (SPG == 1 || (st & 1)) tc_commit(&S.acc_full[b]);
+              tc_commit(bar_empty(s));
+              if (SPG == 1 || (st & 1)) tc_commit(bar_acc_full(b));
             }
           }
           if (SPG == 1 || (st & 1)) ia += n_groups;
