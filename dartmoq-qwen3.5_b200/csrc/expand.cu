@@ -26,6 +26,7 @@ struct ExpandArgs {
   int inter;               // gate_up: rows per member = 2*inter, interleaved; 0 = keep the source order (down)
   void* image;
   float* norm_img;
+  float norm_scale;        // the INT8 image norms carry 2^49 (see dmoq.h: the GEMM reads biased sums as denormals)
 };
 
 __device__ __forceinline__ int source_row(int n_img, int inter) {
@@ -91,7 +92,7 @@ __global__ void __launch_bounds__(256) expand_kernel(ExpandArgs a) {
       *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
     }
     if (c == 0 && a.norm_img != nullptr)
-      a.norm_img[(size_t)g * a.N + n] = __half2float(__ushort_as_half(a.norm[(size_t)g * a.N + ns]));
+      a.norm_img[(size_t)g * a.N + n] = __half2float(__ushort_as_half(a.norm[(size_t)g * a.N + ns])) * a.norm_scale;
   }
 }
 
@@ -131,6 +132,7 @@ extern "C" int dmoq_expand_weights(const dmoq_pool_t* pool, int32_t is_down, int
   a.inter = is_down ? 0 : p.inter;
   a.image = image;
   a.norm_img = norm_image;
+  a.norm_scale = (p.mode == DMOQ_A8) ? DMOQ_A8_NORM_IMAGE_SCALE : 1.0f;
   const long long total = (long long)a.G * a.N * 8;
   long long blocks = (total + 255) / 256;
   const long long cap = 32LL * dmoq_sm_count();

@@ -60,10 +60,24 @@ constexpr int kEpiWarps = 16;
 constexpr int kTileA = kBM * 128;   // bytes of one A operand tile
 constexpr uint32_t kSpinLimit = 1u << 26;
 constexpr long long kWaitCycles = 2000000000LL;
-// INT8 accumulators start from the bit pattern of 1.5*2^23: the int32 sum read back as fp32 is 12582912 + sum
-// exactly (|sum| <= 128*127*127 < 2^22), which saves the integer->float conversion.
-constexpr uint32_t kMagicBits = 0x4B400000u;
-constexpr float kMagicFloat = 12582912.0f;
+// INT8 groups start with a "bias" MMA (accumulate off) of two constant unsigned tiles, so every int32 sum lands in
+// [0, 2^23): such a bit pattern read as fp32 is the denormal (bias + sum) * 2^-149, exactly, and one fused
+// multiply-add removes the bias and applies the row scale: (bias + sum) * 2^-149 * (xs * 2^100) - bias * 2^-49 * xs
+// = sum * xs * 2^-49, rounded like sum * xs itself; the norm image carries the other 2^49.  No integer->float
+// conversion and no accumulator re-initialisation by the epilogue.  The bias needs few significant bits (its
+// product with an 11-bit row scale must be exact in fp32) and must exceed the largest |sum|:
+//   one bias MMA  (K = 32):  2 * sum_16(a_j * b_j) = 0x1F8100 = 2064640 >= 128*127*127   (codeword tables clamp to +-127)
+//   two bias MMAs (K = 64):  4 * sum_16(a_j * b_j) = 2^21             >= 128*127*128   (identity table: -128 occurs)
+// The operand bytes repeat with period 16 along K, so the 128-byte swizzle leaves them where they are, and every
+// row is the same, so one 8-row block of 1 KB serves all rows (stride 0 between 8-row groups in the descriptor).
+constexpr uint32_t kBias1 = 0x1F8100u, kBias2 = 0x200000u;
+constexpr float kXsScale = 1.2676506002282294e30f;           // 2^100
+constexpr float kBiasToOff = 1.7763568394002505e-15f;        // 2^-49
+__constant__ uint8_t kBiasBytes[4][16] = {
+    {253, 229, 255, 255, 255, 255, 255, 255, 255, 255, 255, 255, 255, 255, 255, 255},   // one MMA: A operand
+    {254, 252, 255, 255, 255, 255, 255, 255, 255, 255, 255, 255, 255, 255, 255, 255},   // one MMA: B operand
+    {151, 151, 151, 151, 151, 151, 151, 151, 151, 151, 151, 151, 151, 151, 3, 255},     // two MMAs: A operand
+    {217, 217, 217, 217, 217, 217, 217, 217, 217, 217, 217, 217, 217, 217, 175, 255}};  // two MMAs: B operand
 constexpr int kTmemCols = 512;
 constexpr int kSfaCol = 384;        // FP4 (128-column tiles): three accumulators, then the scale-factor columns
 constexpr int kSfbCol = kSfaCol + kStages * 2 * 4;
@@ -95,6 +109,7 @@ struct ImgPool {
   int n_img;                  // image rows per group
   int inter;                  // intermediate size of the pool's members
   int pool;                   // index into the routing tables' per-pool tile lists
+  int n_bias;                 // A8: bias MMAs per group (1, or 2 when the pool's weight codes reach -128)
 };
 
 struct ImgMaps {
@@ -231,6 +246,14 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
         : "memory");
   }
 }
+// unsigned 8-bit x unsigned 8-bit into the int32 accumulator (the bias MMAs of the INT8 mode)
+__device__ __forceinline__ void tc_mma_u8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // e2m1 x e2m1, one ue8m0 scale per 32 elements of K for each operand, read from TMEM (K = 64 per instruction)
 __device__ __forceinline__ void tc_mma_mxf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
@@ -250,10 +273,6 @@ __device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t (&r)[8]) {
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-// 32 lanes x 8 columns of one value
-__device__ __forceinline__ void tc_st8_fill(uint32_t taddr, uint32_t v) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(taddr), "r"(v) : "memory");
-}
 // 32 lanes x 4 columns: thread t writes its four values to lane base + t
 __device__ __forceinline__ void tc_st4(uint32_t taddr, uint32_t v0, uint32_t v1, uint32_t v2, uint32_t v3) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(v0), "r"(v1), "r"(v2), "r"(v3)
@@ -266,12 +285,6 @@ __device__ __forceinline__ void tc_ld16x16(uint32_t taddr, uint32_t (&r)[8]) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                : "r"(taddr)
                : "memory");
-}
-// 16 lanes x 16 columns of one value (the block of one tc_ld16x16).  A store takes its values from consecutive
-// registers, so two stores of four keep four registers busy with the constant instead of eight.
-__device__ __forceinline__ void tc_st16x16_fill(uint32_t taddr, uint32_t v) {
-  asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1,%1,%1,%1};" ::"r"(taddr), "r"(v) : "memory");
-  asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1,%1,%1,%1};" ::"r"(taddr + 8), "r"(v) : "memory");
 }
 // Pairs of fp32 values live in 64-bit registers from the load to the last fused multiply-add, so that no
 // pack / unpack moves stand between the packed instructions.
@@ -312,10 +325,16 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
+// the same with stride 0 between 8-row groups: every group of rows reads the one 1 KB block at smem_addr
+__device__ __forceinline__ uint64_t make_desc_rows_alias(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
 template <int BN>
 struct Smem {
   uint8_t a[kStages][kTileA];              // 1024-byte aligned operand tiles
   uint8_t b[kStages][Cfg<BN>::kTileB];
+  uint8_t bias[4][1024];                   // A8: constant operand blocks of the bias MMAs (1024-byte aligned)
   float norm[Cfg<BN>::kNormRing][BN];      // column norms of a group, image column order
   uint64_t full[kStages], empty[kStages], acc_full[4], acc_empty[4];
   uint32_t tmem_base;
@@ -384,22 +403,24 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, S.tmem_base, 0);
-  if (MODE == DMOQ_A8 || MODE == DMOQ_FP4) {
-    if (warp < kEpiWarps) {
-      const uint32_t t0 = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-      if (MODE == DMOQ_A8) {   // bias every accumulator buffer: this warp's 32 lanes x its columns of each
-#pragma unroll
-        for (int b = 0; b < ACC; ++b)
-#pragma unroll
-          for (int q = 0; q < 4 * NH; ++q) tc_st8_fill(t0 + b * BN + (warp >> 2) * (32 * NH) + 8 * q, kMagicBits);
-      } else if (warp < 4) {   // the constant weight block scale, for every column and every 32-block of K
-        tc_st4(t0 + kSfbCol, a.sfb_word, a.sfb_word, a.sfb_word, a.sfb_word);
-      }
+  if (MODE == DMOQ_FP4) {
+    if (warp < 4) {   // the constant weight block scale, for every column and every 32-block of K
+      tc_st4(tmem_base + ((uint32_t)(warp * 32) << 16) + kSfbCol, a.sfb_word, a.sfb_word, a.sfb_word, a.sfb_word);
       tc_wait_st();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+  }
+  if (MODE == DMOQ_A8) {   // the bias operand blocks: 16 bytes repeated, visible to the tensor core's reads after the fence
+    for (int i = tid; i < 4 * 1024 / 4; i += C::kThreads) {
+      const int t = i >> 8, j = (i & 3) * 4;
+      const uint32_t w = (uint32_t)kBiasBytes[t][j] | ((uint32_t)kBiasBytes[t][j + 1] << 8) | ((uint32_t)kBiasBytes[t][j + 2] << 16) |
+                         ((uint32_t)kBiasBytes[t][j + 3] << 24);
+      reinterpret_cast<uint32_t*>(&S.bias[0][0])[i] = w;
+    }
+    fence_proxy_async();
+    __syncthreads();
   }
 
   // Work items = (tile, column block) pairs of every pool of the launch, pool after pool; CTA b takes items b, b + grid, ...
@@ -475,6 +496,8 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
       const Item cur = item_of(item);
       const DmoqTile tile = cur.tile;
       const int nb = cur.nb, G = cur.G, inter = a.pp[cur.q].inter;
+      const uint32_t bias_int = a.pp[cur.q].n_bias == 2 ? kBias2 : kBias1;
+      const float bias_off = (float)bias_int * kBiasToOff;
       // thread row r = 2*h + j: tile row lq*32 + 16*h + 8*j + li
       int xoff[4];                                   // element offset of the row's scales (row 0 of the tile for rows past its end)
 #pragma unroll
@@ -490,10 +513,9 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
 #pragma unroll
         for (int r = 0; r < 4; ++r) xraw[r] = xs_tab[xoff[r]];
       }
-      int held = -1;     // accumulator buffer whose release is still owed (its bias stores are in flight)
+      int held = -1;     // accumulator buffer whose release is still owed
       auto release = [&]() {
         if (held >= 0) {
-          if (MODE == DMOQ_A8) tc_wait_st();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_acc_empty((uint32_t)held));
@@ -508,10 +530,12 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
         if (has_xs) {
 #pragma unroll
           for (int r = 0; r < 4; ++r) {
-            const float x = __half2float(__ushort_as_half((unsigned short)xraw[r]));
+            const float x0 = __half2float(__ushort_as_half((unsigned short)xraw[r]));
+            // INT8: the accumulator reads as the denormal (bias + sum) * 2^-149; times xs * 2^100, minus the exact
+            // constant bias * 2^-49 * xs, that is sum * xs * 2^-49 in one rounding.  e4m3: acc * xs.
+            const float x = (MODE == DMOQ_A8) ? x0 * kXsScale : x0;
+            const float o = (MODE == DMOQ_A8) ? -bias_off * x0 : 0.f;
             xs2[r] = pack_x2(__float_as_uint(x), __float_as_uint(x));
-            // INT8: (acc_biased - M) * xs in one fma with the exact constant -M*xs; e4m3: acc * xs
-            const float o = (MODE == DMOQ_A8) ? -kMagicFloat * x : 0.f;
             off2[r] = pack_x2(__float_as_uint(o), __float_as_uint(o));
           }
           if (g + 1 < G) {
@@ -542,11 +566,9 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
             tc_wait_ld();
             PROF_END2(1);   // a part of the chunk loop's time
           }
-          // the previous group's buffer goes back to the MMA thread here: its bias stores were issued a whole group
-          // ago, so waiting for them costs nothing now
+          // the previous group's buffer goes back to the MMA thread here, one group late: nothing waits for it
+          // yet, and this group's first load is already under way
           if (c == 0) release();
-          const uint32_t t_chunk = t_acc + ((c & 1) ? (16u << 16) : 0u) + b * BN + 16 * (c >> 1);
-          if (MODE == DMOQ_A8) tc_st16x16_fill(t_chunk, kMagicBits);   // the chunk has landed: re-arm the bias for the buffer's next use
           if (c + 1 < NCH) tc_ld16x16(t_acc + (((c + 1) & 1) ? (16u << 16) : 0u) + b * BN + 16 * ((c + 1) >> 1), v[(c + 1) & 1]);
           const uint32_t(&vc)[8] = v[c & 1];
 #pragma unroll
@@ -568,7 +590,7 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
                 const int n = a.is_down ? nb * BN + cbase + col
                                         : (col < 16 ? 0 : inter) + nb * (BN / 2) + cq * 16 + (col & 15);
                 if (row < tile.rows)
-                  a.partials[((size_t)(tile.row0 + row) * n_out + n) * G + g] = (int32_t)(vc[2 * p + e] - kMagicBits);
+                  a.partials[((size_t)(tile.row0 + row) * n_out + n) * G + g] = (int32_t)(vc[2 * p + e] - bias_int);
               }
             }
           }
@@ -682,7 +704,7 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
         for (int st = 0; st < steps_per_item; ++st, ++it) {
           const int s = it % kStages;
           PROF_BEGIN();
-          mbar_wait<200>(bar_empty(s), ((it / kStages) & 1) ^ 1, abort_flag);
+          mbar_wait<400>(bar_empty(s), ((it / kStages) & 1) ^ 1, abort_flag);
           PROF_END(0);
           PROF_BEGIN();
           if (loader) {
@@ -745,6 +767,7 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
       // ========================================================================= MMA warp
       constexpr uint32_t nm = ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
       constexpr uint32_t idesc_i8 = (2u << 4) | (1u << 7) | (1u << 10) | nm;    // s32 accumulate, signed 8-bit operands
+      constexpr uint32_t idesc_u8 = (2u << 4) | nm;                              // s32 accumulate, unsigned 8-bit operands
       constexpr uint32_t idesc_f8 = (1u << 4) | nm;                              // f32 accumulate, e4m3 operands
       constexpr uint32_t idesc_f16 = (1u << 4) | nm;                             // f32 accumulate, fp16 operands
       constexpr uint32_t idesc_f4 = (1u << 7) | (1u << 10) | (1u << 23) | nm;    // e2m1 operands, ue8m0 scales, K = 64
@@ -755,12 +778,14 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
 #endif
       for (int item = 0; item < n_items; ++item) {
         int start_unused;
-        const int G = groups_of(pool_of_item(item, start_unused));
+        const int q_item = pool_of_item(item, start_unused);
+        const int G = groups_of(q_item);
+        const int n_bias = a.pp[q_item].n_bias;
         const int steps_per_item = steps_of(G);
         for (int st = 0; st < steps_per_item; ++st, ++it) {
           const int s = it % kStages;
           PROF_BEGIN();
-          bool ok = mbar_wait<40>(bar_full(s), (it / kStages) & 1, abort_flag);
+          bool ok = mbar_wait<64>(bar_full(s), (it / kStages) & 1, abort_flag);
           PROF_END(0);
           PROF_BEGIN();
           const int n_groups = (SPG == 2) ? 1 : min(GPS, G - st * GPS);
@@ -768,7 +793,7 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
           if (SPG == 1 || (st & 1) == 0) {
             for (int j = 0; j < n_groups; ++j) {
               const uint32_t ib = ia + j;
-              ok = mbar_wait<40>(bar_acc_empty(ib % ACC), ((ib / ACC) & 1) ^ 1, abort_flag) && ok;
+              ok = mbar_wait<64>(bar_acc_empty(ib % ACC), ((ib / ACC) & 1) ^ 1, abort_flag) && ok;
             }
           }
           PROF_END(1);
@@ -792,9 +817,14 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
             } else {
               const uint32_t b = ia % ACC;
               const uint32_t d = tmem_base + b * BN;
+              if (MODE == DMOQ_A8) {   // the group's sums start from the bias: constant unsigned blocks, accumulate off
+                const uint32_t blk = sb + (uint32_t)offsetof(SM, bias) + (n_bias == 2 ? 2048u : 0u);
+                const uint64_t ba = make_desc_rows_alias(blk), bb = make_desc_rows_alias(blk + 1024u);
+                for (int j = 0; j < n_bias; ++j) tc_mma_u8(d, ba, bb, idesc_u8, j > 0);
+              }
 #pragma unroll
               for (int k = 0; k < 4; ++k) {  // 32 bytes of K per instruction: +2 in 16-byte units
-                if (MODE == DMOQ_A8) tc_mma<DMOQ_A8>(d, da + 2 * k, db + 2 * k, idesc_i8, 1);  // the buffer holds the bias
+                if (MODE == DMOQ_A8) tc_mma<DMOQ_A8>(d, da + 2 * k, db + 2 * k, idesc_i8, 1);  // on top of the bias
                 else if (MODE == DMOQ_FP8) tc_mma<DMOQ_FP8>(d, da + 2 * k, db + 2 * k, idesc_f8, k > 0);
                 else tc_mma<DMOQ_A16>(d, da + 2 * k, db + 2 * k, idesc_f16, ((st & 1) || k > 0) ? 1u : 0u);
               }
@@ -931,6 +961,7 @@ int dmoq_grouped_gemm_img_pools(const dmoq_route_t* route, const dmoq_pool_t* po
     pp.n_img = is_down ? hidden : p.n_members * 2 * p.inter;
     pp.inter = p.inter;
     pp.pool = pool_ids[i];
+    pp.n_bias = (mode == DMOQ_A8 && p.identity_lut) ? 2 : 1;
     const int groups = is_down ? p.n_members * p.inter / kG : hidden / kG;
     // image geometry: rows of 128 elements (256 bytes as fp16, 128 bytes otherwise); e2m1 rows hold two groups
     size_t rows, row_bytes;

@@ -47,6 +47,9 @@ enum {
   DMOQ_EPI_PLAIN = 2     /* store fp16(acc); gate_up form: (R, 2*inter) = [gate | up]      */
 };
 
+/* factor carried by the fp32 norm images of A8 pools (2^49, exact) */
+#define DMOQ_A8_NORM_IMAGE_SCALE 562949953421312.0f
+
 #define DMOQ_GROUP 128      /* quantisation group = rotation block, fixed by the format */
 #define DMOQ_MAX_POOLS 8
 
@@ -274,7 +277,9 @@ int dmoq_widen_indices(const uint8_t* packed, int64_t n_bytes, int32_t bit, uint
 
 /*
  * Weight image of one pool and one projection (is_down 0: gate_up, 1: down) for dmoq_pool_t.gu_img / dn_img, and its
- * fp32 column norms for gu_norm_img / dn_norm_img (norm_image may be NULL when only the codewords change).  Every
+ * fp32 column norms for gu_norm_img / dn_norm_img (norm_image may be NULL when only the codewords change).  In the A8
+ * mode the norm image holds the norms times DMOQ_A8_NORM_IMAGE_SCALE (an exact power of two: the image GEMM reads its
+ * biased int32 sums as fp32 denormals and splits the compensating 2^149 between the row scale and the column norm).  Every
  * codebook index is looked up in the pool's mode table once, here, instead of once per 128-row tile in the GEMM:
  *   A8 / FP8 (G, N, 128) bytes, A16 (G, N, 128) fp16, FP4 (ceil(G/2), N, 128) bytes = two groups of packed e2m1 per
  *   row, which is the reference's load-time fold (turboquant_utils/triton_kernels_fp4.py:80-127,
