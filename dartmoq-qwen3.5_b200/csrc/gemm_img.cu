@@ -129,6 +129,7 @@ struct ImgArgs {
   void* out;
   int out_stride;
   int32_t* partials;
+  int out_lines;              // the output rows are 16-byte aligned: the down epilogue may store whole lines
   uint32_t sfb_word;          // FP4: the weight block scale byte 127+E0 replicated four times
 };
 
@@ -286,6 +287,17 @@ __device__ __forceinline__ void tc_ld16x16(uint32_t taddr, uint32_t (&r)[8]) {
                : "r"(taddr)
                : "memory");
 }
+// Four 8x8 matrices of 16-bit values from accumulator-fragment registers (thread t holds row t/4, columns 2(t%4),
+// 2(t%4)+1 of each) to shared memory; thread t supplies the address of row t%8 of matrix t/8 (16 bytes per row).
+__device__ __forceinline__ void stmatrix_x4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
 // Pairs of fp32 values live in 64-bit registers from the load to the last fused multiply-add, so that no
 // pack / unpack moves stand between the packed instructions.
 typedef unsigned long long f32x2_t;
@@ -336,6 +348,7 @@ struct Smem {
   uint8_t b[kStages][Cfg<BN>::kTileB];
   uint8_t bias[4][1024];                   // A8: constant operand blocks of the bias MMAs (1024-byte aligned)
   float norm[Cfg<BN>::kNormRing][BN];      // column norms of a group, image column order
+  uint8_t stage[kEpiWarps][1024];          // per epilogue warp: 8 output rows on their way from fragments to full lines
   uint64_t full[kStages], empty[kStages], acc_full[4], acc_empty[4];
   uint32_t tmem_base;
   int abort_flag;
@@ -654,7 +667,38 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
           }
           return bits;
         };
-        if (a.is_down) {   // tile columns are output columns
+        if (a.is_down && a.out_lines) {
+          // Down rows leave as full lines: per round (h, j) the warp's 8 rows x 32*NH columns go through a small
+          // staging block (stmatrix turns the fragments into rows, 16-byte chunks XOR-swizzled against bank
+          // conflicts) and come back 16 bytes per thread, so one store instruction covers whole 64*NH-byte row
+          // segments instead of eight 16-byte pieces.
+          constexpr int CH = 4 * NH;                                   // 16-byte chunks per staged row
+          const uint32_t stage = sb + (uint32_t)offsetof(SM, stage) + 1024u * (uint32_t)warp;
+          const int sr = lane & 7, smi = lane >> 3;                    // stmatrix: this lane addresses row sr of matrix smi
+          uint16_t* const obase = reinterpret_cast<uint16_t*>(a.out) + (size_t)tile.row0 * a.out_stride + nb * BN + cbase;
+#pragma unroll
+          for (int hj = 0; hj < 4; ++hj) {
+            const int h = hj >> 1, j = hj & 1;
+            uint32_t w[CH];
+#pragma unroll
+            for (int mi = 0; mi < CH; ++mi) w[mi] = out_bits(2 * (mi >> 1) + h, j + 2 * (mi & 1));   // matrix mi = 2k + m
+            __syncwarp();                                              // the previous round has been read back
+#pragma unroll
+            for (int gi = 0; gi < CH / 4; ++gi) {
+              const int mi = 4 * gi + smi;
+              const int pc = mi ^ ((CH == 8) ? sr : (sr >> 1));
+              stmatrix_x4(stage + (uint32_t)(sr * (CH * 16) + pc * 16), w[4 * gi], w[4 * gi + 1], w[4 * gi + 2], w[4 * gi + 3]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < CH / 4; ++i) {
+              const int u = i * 32 + lane, r = u / CH, cl = u % CH;
+              const uint4 v4 = lds_v4(stage + (uint32_t)(r * (CH * 16) + ((cl ^ ((CH == 8) ? r : (r >> 1))) * 16)));
+              const int row = lq * 32 + 16 * h + 8 * j + r;
+              if (row < tile.rows) *reinterpret_cast<uint4*>(obase + (size_t)row * a.out_stride + cl * 8) = v4;
+            }
+          }
+        } else if (a.is_down) {   // tile columns are output columns
 #pragma unroll
           for (int c = 0; c < NCH; ++c)
 #pragma unroll
@@ -948,6 +992,7 @@ int dmoq_grouped_gemm_img_pools(const dmoq_route_t* route, const dmoq_pool_t* po
   a.out = out;
   a.out_stride = out_stride;
   a.partials = partials;
+  a.out_lines = (out_stride % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) ? 1 : 0;
   // 256-column tiles wherever the shape allows (not FP4: its scale-factor columns share TMEM with the accumulators)
   bool wide = mode != DMOQ_FP4 && partials == nullptr && (is_down ? hidden % 256 == 0 : true);
   for (int i = 0; i < n_ids; ++i) wide = wide && (is_down || pools[pool_ids[i]].inter % 128 == 0);
