@@ -298,6 +298,29 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
   return v;
 }
+// Eight output rows of a warp leave as full lines: CH 8x8 matrices of fp16 pairs (w[mi]: this thread's pair of matrix
+// mi, accumulator-fragment layout) go through the warp's staging block, 16-byte chunks XOR-swizzled against bank
+// conflicts, and come back 16 bytes per thread, so one store instruction covers whole row segments of 16*CH bytes
+// instead of eight 16-byte pieces.  Row r of the eight is stored to dst + r * stride if r < rows_left.
+template <int CH>
+__device__ __forceinline__ void store_rows_staged(uint32_t stage, int lane, const uint32_t (&w)[CH], uint16_t* dst, size_t stride,
+                                                  int rows_left) {
+  static_assert(CH == 4 || CH == 8, "four or eight 16-byte chunks per staged row");
+  const int sr = lane & 7, smi = lane >> 3;                    // stmatrix: this lane addresses row sr of matrix smi
+  __syncwarp();                                                // the previous use of the block has been read back
+#pragma unroll
+  for (int gi = 0; gi < CH / 4; ++gi) {
+    const int pc = (4 * gi + smi) ^ ((CH == 8) ? sr : (sr >> 1));
+    stmatrix_x4(stage + (uint32_t)(sr * (CH * 16) + pc * 16), w[4 * gi], w[4 * gi + 1], w[4 * gi + 2], w[4 * gi + 3]);
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < CH / 4; ++i) {
+    const int u = i * 32 + lane, r = u / CH, cl = u % CH;
+    const uint4 v4 = lds_v4(stage + (uint32_t)(r * (CH * 16) + ((cl ^ ((CH == 8) ? r : (r >> 1))) * 16)));
+    if (r < rows_left) *reinterpret_cast<uint4*>(dst + (size_t)r * stride + cl * 8) = v4;
+  }
+}
 // Pairs of fp32 values live in 64-bit registers from the load to the last fused multiply-add, so that no
 // pack / unpack moves stand between the packed instructions.
 typedef unsigned long long f32x2_t;
@@ -628,25 +651,41 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
           rowp[r] = reinterpret_cast<uint16_t*>(a.out) + (size_t)(tile.row0 + row) * a.out_stride + col0;
         }
       }
+      const uint32_t stage = sb + (uint32_t)offsetof(SM, stage) + 1024u * (uint32_t)warp;
       if (EPI == DMOQ_EPI_SILU) {
         // image columns [0,16) of a 32-column block = gate, [16,32) = up of 16 consecutive outputs: chunks 2*h2 and
         // 2*h2 + 1 hold a thread's gate and up values at the same positions
+        auto silu_bits = [&](int h2, int h, int p) {
+          const float2 gt = unpack_x2(total2[(4 * h2 + h) * 4 + p]), ut = unpack_x2(total2[(4 * h2 + 2 + h) * 4 + p]);
+          const __half2 uh = __floats2half2_rn(ut.x, ut.y);                       // fp16 up
+          const float2 gf = __half22float2(__floats2half2_rn(gt.x, gt.y));        // fp16 gate, back in fp32
+          // fast exp and reciprocal (a few fp32 ulps) ahead of the fp16 rounding: a floating-point stage
+          const __half2 sg = __floats2half2_rn(__fdividef(gf.x, 1.0f + __expf(-gf.x)), __fdividef(gf.y, 1.0f + __expf(-gf.y)));
+          // fp16(silu * up): the product of two fp16 values is exact in fp32, so one fp16 multiply rounds the same
+          const __half2 o2 = __hmul2(sg, uh);
+          return *reinterpret_cast<const uint32_t*>(&o2);
+        };
+        if (NH == 2 && a.out_lines) {   // the warp's 8 rows x 32 outputs per round: matrix mi = 2*h2 + m
+          uint16_t* const obase = reinterpret_cast<uint16_t*>(a.out) + (size_t)tile.row0 * a.out_stride + nb * (BN / 2) + cq * NH * 16;
 #pragma unroll
-        for (int h2 = 0; h2 < NH; ++h2)
+          for (int hj = 0; hj < 4; ++hj) {
+            const int h = hj >> 1, j = hj & 1, row = lq * 32 + 16 * h + 8 * j;
+            uint32_t w[4];
 #pragma unroll
-          for (int h = 0; h < 2; ++h)
+            for (int mi = 0; mi < 4; ++mi) w[mi] = silu_bits(mi >> 1, h, j + 2 * (mi & 1));
+            store_rows_staged<4>(stage, lane, w, obase + (size_t)row * a.out_stride, a.out_stride, tile.rows - row);
+          }
+        } else {
 #pragma unroll
-            for (int p = 0; p < 4; ++p) {
-              const float2 gt = unpack_x2(total2[(4 * h2 + h) * 4 + p]), ut = unpack_x2(total2[(4 * h2 + 2 + h) * 4 + p]);
-              const __half2 uh = __floats2half2_rn(ut.x, ut.y);                       // fp16 up
-              const float2 gf = __half22float2(__floats2half2_rn(gt.x, gt.y));        // fp16 gate, back in fp32
-              // fast exp and reciprocal (a few fp32 ulps) ahead of the fp16 rounding: a floating-point stage
-              const __half2 sg = __floats2half2_rn(__fdividef(gf.x, 1.0f + __expf(-gf.x)), __fdividef(gf.y, 1.0f + __expf(-gf.y)));
-              // fp16(silu * up): the product of two fp16 values is exact in fp32, so one fp16 multiply rounds the same
-              const __half2 o2 = __hmul2(sg, uh);
-              const int r = 2 * h + (p & 1);
-              if (live[r]) *reinterpret_cast<uint32_t*>(rowp[r] + h2 * 16 + 8 * (p >> 1)) = *reinterpret_cast<const uint32_t*>(&o2);
-            }
+          for (int h2 = 0; h2 < NH; ++h2)
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int p = 0; p < 4; ++p) {
+                const int r = 2 * h + (p & 1);
+                if (live[r]) *reinterpret_cast<uint32_t*>(rowp[r] + h2 * 16 + 8 * (p >> 1)) = silu_bits(h2, h, p);
+              }
+        }
       } else {
         float wgt[4] = {0.f, 0.f, 0.f, 0.f};
         if (EPI == DMOQ_EPI_WEIGHTED) {
@@ -668,35 +707,15 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
           return bits;
         };
         if (a.is_down && a.out_lines) {
-          // Down rows leave as full lines: per round (h, j) the warp's 8 rows x 32*NH columns go through a small
-          // staging block (stmatrix turns the fragments into rows, 16-byte chunks XOR-swizzled against bank
-          // conflicts) and come back 16 bytes per thread, so one store instruction covers whole 64*NH-byte row
-          // segments instead of eight 16-byte pieces.
-          constexpr int CH = 4 * NH;                                   // 16-byte chunks per staged row
-          const uint32_t stage = sb + (uint32_t)offsetof(SM, stage) + 1024u * (uint32_t)warp;
-          const int sr = lane & 7, smi = lane >> 3;                    // stmatrix: this lane addresses row sr of matrix smi
+          // per round (h, j): the warp's 8 rows x 32*NH columns; matrix mi = 2k + m holds columns 16k + 8m .. +7
           uint16_t* const obase = reinterpret_cast<uint16_t*>(a.out) + (size_t)tile.row0 * a.out_stride + nb * BN + cbase;
 #pragma unroll
           for (int hj = 0; hj < 4; ++hj) {
-            const int h = hj >> 1, j = hj & 1;
-            uint32_t w[CH];
+            const int h = hj >> 1, j = hj & 1, row = lq * 32 + 16 * h + 8 * j;
+            uint32_t w[4 * NH];
 #pragma unroll
-            for (int mi = 0; mi < CH; ++mi) w[mi] = out_bits(2 * (mi >> 1) + h, j + 2 * (mi & 1));   // matrix mi = 2k + m
-            __syncwarp();                                              // the previous round has been read back
-#pragma unroll
-            for (int gi = 0; gi < CH / 4; ++gi) {
-              const int mi = 4 * gi + smi;
-              const int pc = mi ^ ((CH == 8) ? sr : (sr >> 1));
-              stmatrix_x4(stage + (uint32_t)(sr * (CH * 16) + pc * 16), w[4 * gi], w[4 * gi + 1], w[4 * gi + 2], w[4 * gi + 3]);
-            }
-            __syncwarp();
-#pragma unroll
-            for (int i = 0; i < CH / 4; ++i) {
-              const int u = i * 32 + lane, r = u / CH, cl = u % CH;
-              const uint4 v4 = lds_v4(stage + (uint32_t)(r * (CH * 16) + ((cl ^ ((CH == 8) ? r : (r >> 1))) * 16)));
-              const int row = lq * 32 + 16 * h + 8 * j + r;
-              if (row < tile.rows) *reinterpret_cast<uint4*>(obase + (size_t)row * a.out_stride + cl * 8) = v4;
-            }
+            for (int mi = 0; mi < 4 * NH; ++mi) w[mi] = out_bits(2 * (mi >> 1) + h, j + 2 * (mi & 1));
+            store_rows_staged<4 * NH>(stage, lane, w, obase + (size_t)row * a.out_stride, a.out_stride, tile.rows - row);
           }
         } else if (a.is_down) {   // tile columns are output columns
 #pragma unroll
