@@ -549,16 +549,6 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
 #pragma unroll
         for (int r = 0; r < 4; ++r) xraw[r] = xs_tab[xoff[r]];
       }
-      int held = -1;     // accumulator buffer whose release is still owed
-      auto release = [&]() {
-        if (held >= 0) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_acc_empty((uint32_t)held));
-          held = -1;
-        }
-      };
-
       for (int g = 0; g < G; ++g, ++ia) {
         const uint32_t b = ia % ACC, ph = (ia / ACC) & 1;
         const uint32_t nrm = norm_u32 + (ia % kNormRing) * (uint32_t)(BN * 4);
@@ -602,10 +592,15 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
             tc_wait_ld();
             PROF_END2(1);   // a part of the chunk loop's time
           }
-          // the previous group's buffer goes back to the MMA thread here, one group late: nothing waits for it
-          // yet, and this group's first load is already under way
-          if (c == 0) release();
-          if (c + 1 < NCH) tc_ld16x16(t_acc + (((c + 1) & 1) ? (16u << 16) : 0u) + b * BN + 16 * ((c + 1) >> 1), v[(c + 1) & 1]);
+          if (c + 1 < NCH) {
+            tc_ld16x16(t_acc + (((c + 1) & 1) ? (16u << 16) : 0u) + b * BN + 16 * ((c + 1) >> 1), v[(c + 1) & 1]);
+          } else {
+            // the group's last chunk is in registers: the buffer goes back to the MMA thread, which gets the time of
+            // this chunk's math and of a whole group on the other buffer to refill it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty(b));
+          }
           const uint32_t(&vc)[8] = v[c & 1];
 #pragma unroll
           for (int p = 0; p < 4; ++p) {   // p = j + 2m
@@ -632,9 +627,7 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
           }
         }
         PROF_END(2);
-        held = (int)b;
       }
-      release();   // before the tile's output stores: the MMA thread may run ahead into the next item
       PROF_BEGIN();
 
       // ---- tile epilogue: a thread stores pairs of adjacent columns (4 bytes); the four threads of a quad fill 16
@@ -767,7 +760,7 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
         for (int st = 0; st < steps_per_item; ++st, ++it) {
           const int s = it % kStages;
           PROF_BEGIN();
-          mbar_wait<400>(bar_empty(s), ((it / kStages) & 1) ^ 1, abort_flag);
+          mbar_wait<500>(bar_empty(s), ((it / kStages) & 1) ^ 1, abort_flag);
           PROF_END(0);
           PROF_BEGIN();
           if (loader) {
@@ -848,7 +841,7 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
         for (int st = 0; st < steps_per_item; ++st, ++it) {
           const int s = it % kStages;
           PROF_BEGIN();
-          bool ok = mbar_wait<64>(bar_full(s), (it / kStages) & 1, abort_flag);
+          bool ok = mbar_wait<100>(bar_full(s), (it / kStages) & 1, abort_flag);
           PROF_END(0);
           PROF_BEGIN();
           const int n_groups = (SPG == 2) ? 1 : min(GPS, G - st * GPS);
@@ -856,7 +849,7 @@ __global__ void __launch_bounds__(Cfg<BN>::kThreads, 1) gemm_img_kernel(const __
           if (SPG == 1 || (st & 1) == 0) {
             for (int j = 0; j < n_groups; ++j) {
               const uint32_t ib = ia + j;
-              ok = mbar_wait<64>(bar_acc_empty(ib % ACC), ((ib / ACC) & 1) ^ 1, abort_flag) && ok;
+              ok = mbar_wait<250>(bar_acc_empty(ib % ACC), ((ib / ACC) & 1) ^ 1, abort_flag) && ok;
             }
           }
           PROF_END(1);
