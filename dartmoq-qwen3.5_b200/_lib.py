@@ -57,6 +57,8 @@ EXPORTS = {
                                    C.c_void_p, C.c_size_t, C.c_void_p]),
     "dmoq_router_topk": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
                                    C.c_void_p]),
+    "dmoq_router_topk_gate": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                        C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p]),
     "dmoq_route_static_max_bytes": (C.c_size_t, []),
     "dmoq_route_build_static": (C.c_int, [C.POINTER(Route), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "dmoq_rotate_quant": (C.c_int, [C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,

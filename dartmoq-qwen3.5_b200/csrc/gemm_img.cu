@@ -10,15 +10,20 @@
 //   triton_kernels_fp8.py:532 (FP8), triton_kernels_fp4.py:587 (FP4: e2m1 x e2m1 with per-32 e8m0 block scales,
 //   weights folded to e2m1 at load time, W_FOLDED).
 //
-// One persistent CTA of 768 threads per SM:
-//   warps 0-15   epilogue: warp w drains lanes 32*(w%4).. of columns 32*(w/4).. of the group's accumulator
-//                (tcgen05.ld 32x32b: a thread owns one row), folds (acc * row_scale) * col_norm into an fp32 running
-//                total, and at the end of a tile writes SiLU*up / plain / weighted rows straight to global memory
-//   warp 16      loader: one thread issues, per operand step, the TMA copies of the A tile (128 rows of the sorted
+// One persistent CTA per SM (640 threads with 256-column tiles, 768 with 128-column tiles):
+//   warps 0-15   epilogue: warp w owns lanes 32*(w%4).. and columns 32*NH*(w/4).. of the group's accumulator and reads
+//                them in the 16x256b shape: a thread holds four rows (i, i+8, i+16, i+24 of the lane quarter) and
+//                16*NH columns, so a group costs it 16*NH column norms (64-bit shared loads, four addresses per warp)
+//                and four row scales; (acc * row_scale) * col_norm goes into fp32 running totals as packed f32x2
+//                fused multiply-adds on 64-bit registers; the buffer returns to the MMA thread as soon as its last
+//                chunk is in registers.  At the end of a tile the fragments pass through a small swizzled staging
+//                block (stmatrix) and leave as full lines: SiLU*up / plain / weighted rows.
+//   loader warp  one thread issues, per operand step, the TMA copies of the A tile (128 rows of the routed-order
 //                activation-code table) and of the B tile, and the bulk copy of the group's column norms
-//   warps 16-19  FP4 mode only: store the rows' e8m0 block scales into TMEM (tcgen05.st) for the block-scaled MMA
-//   warp 20      one thread issues tcgen05.mma: kind::i8 / f8f6f4 / f16, or kind::mxf4nvf4.block_scale (scale_vec 2X)
-//   warps 21-23  idle (setmaxnreg moves their registers to the epilogue)
+//   FP4 only     four warps store the rows' e8m0 block scales into TMEM (tcgen05.st) for the block-scaled MMA
+//   MMA warp     one thread issues tcgen05.mma: kind::i8 / f8f6f4 / f16, or kind::mxf4nvf4.block_scale (scale_vec 2X);
+//                an INT8 group starts with one or two MMAs of constant unsigned tiles (the "bias", see kBias1)
+// All shared-memory operands are 32-bit shared-window addresses derived from one base kept opaque to the optimiser.
 // Every mbarrier wait is bounded; on a timeout the CTA raises the device status word, stops issuing work and
 // falls through to the common teardown, where TMEM is released.
 #include <cuda.h>

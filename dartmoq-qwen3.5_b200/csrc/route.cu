@@ -446,10 +446,28 @@ extern "C" int dmoq_route_build_static(const dmoq_route_t* route, const int64_t*
 // expert index first), optionally renormalised to sum 1.  One warp per token, NPL logits per lane in registers.
 namespace {
 
+// The shared expert's gate for the same token, when asked for: sigmoid(x[t] . w + b) with the roundings of a 16-bit
+// Linear followed by a 16-bit sigmoid (quantization/wxa16/bit_partitioned_moe.py:1101-1106): fp32 dot product,
+// rounded to the activation type, sigmoid in fp32, rounded again; stored as fp32.
+struct SharedGate {
+  const uint16_t* x;       // (T, H) bf16 / fp16 rows, 16-byte aligned, H a multiple of 8; NULL = no shared gate
+  const uint16_t* w;       // (H) same type
+  float bias;
+  int H, is_bf16;
+  float* out;              // (T)
+};
+
+__device__ __forceinline__ float gate_elem(uint16_t bits, int is_bf16) {
+  return is_bf16 ? __uint_as_float((uint32_t)bits << 16) : __half2float(__ushort_as_half(bits));
+}
+__device__ __forceinline__ float gate_round(float v, int is_bf16) {
+  return is_bf16 ? __bfloat162float(__float2bfloat16_rn(v)) : __half2float(__float2half_rn(v));
+}
+
 template <int NPL>
 __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restrict__ logits, int T, int E, int k,
                                                           int renormalize, float* __restrict__ topk_w,
-                                                          int64_t* __restrict__ topk_idx) {
+                                                          int64_t* __restrict__ topk_idx, SharedGate sg) {
   const int lane = threadIdx.x & 31;
   const int warps_per_grid = gridDim.x * (blockDim.x >> 5);
   for (int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < T; t += warps_per_grid) {
@@ -508,30 +526,63 @@ __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restric
       topk_w[(size_t)t * k + lane] = renormalize ? __fdiv_rn(my_w, top_sum) : my_w;
       topk_idx[(size_t)t * k + lane] = my_e;
     }
+    if (sg.x != nullptr) {
+      const uint4* xr = reinterpret_cast<const uint4*>(sg.x + (size_t)t * sg.H);
+      const uint4* wr = reinterpret_cast<const uint4*>(sg.w);
+      float dot = 0.f;
+      for (int c = lane; c < sg.H / 8; c += 32) {
+        const uint4 xv = xr[c], wv = wr[c];
+        const uint16_t* xe = reinterpret_cast<const uint16_t*>(&xv);
+        const uint16_t* we = reinterpret_cast<const uint16_t*>(&wv);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) dot = fmaf(gate_elem(xe[q], sg.is_bf16), gate_elem(we[q], sg.is_bf16), dot);
+      }
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);
+      if (lane == 0) {
+        const float g = gate_round(dot + sg.bias, sg.is_bf16);
+        sg.out[t] = gate_round(1.0f / (1.0f + expf(-g)), sg.is_bf16);
+      }
+    }
   }
 }
 
 template <int NPL>
-int launch_router(const float* logits, int T, int E, int k, int renorm, float* w, int64_t* idx, cudaStream_t s) {
+int launch_router(const float* logits, int T, int E, int k, int renorm, float* w, int64_t* idx, const SharedGate& sg, cudaStream_t s) {
   int blocks = dmoq_ceil_div(T, 8);
   const int cap = 16 * dmoq_sm_count();
   if (blocks > cap) blocks = cap;
-  router_topk_kernel<NPL><<<blocks, 256, 0, s>>>(logits, T, E, k, renorm, w, idx);
+  router_topk_kernel<NPL><<<blocks, 256, 0, s>>>(logits, T, E, k, renorm, w, idx, sg);
   return dmoq_launch_status();
 }
 
 }  // namespace
+
+static int router_dispatch(const float* logits, int T, int E, int top_k, int renormalize, float* topk_w, int64_t* topk_idx,
+                    const SharedGate& sg, cudaStream_t s) {
+  if (E <= 32) return launch_router<1>(logits, T, E, top_k, renormalize, topk_w, topk_idx, sg, s);
+  if (E <= 64) return launch_router<2>(logits, T, E, top_k, renormalize, topk_w, topk_idx, sg, s);
+  if (E <= 128) return launch_router<4>(logits, T, E, top_k, renormalize, topk_w, topk_idx, sg, s);
+  if (E <= 256) return launch_router<8>(logits, T, E, top_k, renormalize, topk_w, topk_idx, sg, s);
+  if (E <= 512) return launch_router<16>(logits, T, E, top_k, renormalize, topk_w, topk_idx, sg, s);
+  return launch_router<32>(logits, T, E, top_k, renormalize, topk_w, topk_idx, sg, s);
+}
 
 extern "C" int dmoq_router_topk(const float* logits, int32_t T, int32_t E, int32_t top_k, int32_t renormalize,
                                 float* topk_w, int64_t* topk_idx, void* stream) {
   DMOQ_CHECK_ARG(logits && topk_w && topk_idx && T >= 0);
   DMOQ_CHECK_ARG(E > 0 && E <= 1024 && top_k > 0 && top_k <= 32 && top_k <= E);
   if (T == 0) return DMOQ_OK;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (E <= 32) return launch_router<1>(logits, T, E, top_k, renormalize, topk_w, topk_idx, s);
-  if (E <= 64) return launch_router<2>(logits, T, E, top_k, renormalize, topk_w, topk_idx, s);
-  if (E <= 128) return launch_router<4>(logits, T, E, top_k, renormalize, topk_w, topk_idx, s);
-  if (E <= 256) return launch_router<8>(logits, T, E, top_k, renormalize, topk_w, topk_idx, s);
-  if (E <= 512) return launch_router<16>(logits, T, E, top_k, renormalize, topk_w, topk_idx, s);
-  return launch_router<32>(logits, T, E, top_k, renormalize, topk_w, topk_idx, s);
+  return router_dispatch(logits, T, E, top_k, renormalize, topk_w, topk_idx, SharedGate{}, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int dmoq_router_topk_gate(const float* logits, int32_t T, int32_t E, int32_t top_k, int32_t renormalize,
+                                     float* topk_w, int64_t* topk_idx, const void* x, int32_t x_is_bf16, int32_t hidden,
+                                     const void* gate_w, float gate_bias, float* shared_w, void* stream) {
+  DMOQ_CHECK_ARG(logits && topk_w && topk_idx && T >= 0 && x && gate_w && shared_w);
+  DMOQ_CHECK_ARG(E > 0 && E <= 1024 && top_k > 0 && top_k <= 32 && top_k <= E);
+  DMOQ_CHECK_ARG(hidden > 0 && hidden % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(gate_w) % 16 == 0);
+  if (T == 0) return DMOQ_OK;
+  SharedGate sg{static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(gate_w), gate_bias, hidden, x_is_bf16, shared_w};
+  return router_dispatch(logits, T, E, top_k, renormalize, topk_w, topk_idx, sg, static_cast<cudaStream_t>(stream));
 }

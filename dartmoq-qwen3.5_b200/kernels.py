@@ -188,17 +188,37 @@ class _HostRoute:
 
 
 @_on_tensor_device
-def router_topk(logits: torch.Tensor, top_k: int, renormalize: bool = False):
+def router_topk(logits: torch.Tensor, top_k: int, renormalize: bool = False, *, x: Optional[torch.Tensor] = None,
+                shared_gate: Optional[torch.nn.Module] = None):
     """fp32 softmax over experts -> top-k probabilities (descending) and indices (int64), optionally renormalised:
-    the router stage of the module (quantization/wxa16/bit_partitioned_moe.py:1113-1119) as one launch."""
+    the router stage of the module (quantization/wxa16/bit_partitioned_moe.py:1113-1119) as one launch.
+    With ``x`` (T, H) and ``shared_gate`` (a 16-bit ``Linear(H, 1)``) the launch also returns
+    ``sigmoid(shared_gate(x))`` per token as fp32 (module :1101-1106); see :func:`fusable_shared_gate`."""
     _need_cuda(logits)
     lg = logits.to(torch.float32).contiguous()
     T, E = lg.shape
     w = torch.empty((T, top_k), dtype=torch.float32, device=lg.device)
     idx = torch.empty((T, top_k), dtype=torch.int64, device=lg.device)
-    check(_lib.load().dmoq_router_topk(ptr(lg), T, E, top_k, int(renormalize), ptr(w), ptr(idx), _stream()),
-          "dmoq_router_topk")
-    return w, idx
+    if shared_gate is None:
+        check(_lib.load().dmoq_router_topk(ptr(lg), T, E, top_k, int(renormalize), ptr(w), ptr(idx), _stream()),
+              "dmoq_router_topk")
+        return w, idx
+    sw = torch.empty((T,), dtype=torch.float32, device=lg.device)
+    bias = float(shared_gate.bias.float().item()) if shared_gate.bias is not None else 0.0
+    check(_lib.load().dmoq_router_topk_gate(ptr(lg), T, E, top_k, int(renormalize), ptr(w), ptr(idx), ptr(x),
+                                            int(x.dtype == torch.bfloat16), x.shape[-1], ptr(shared_gate.weight), bias,
+                                            ptr(sw), _stream()), "dmoq_router_topk_gate")
+    return w, idx, sw
+
+
+def fusable_shared_gate(gate, x: torch.Tensor) -> bool:
+    """True when ``sigmoid(gate(x))`` can ride in the router launch: a bias-free ``Linear(H, 1)`` whose weight has
+    the activations' 16-bit type and device, rows of x contiguous and 16-byte aligned."""
+    w = getattr(gate, "weight", None)
+    return (isinstance(gate, torch.nn.Linear) and gate.out_features == 1 and gate.bias is None and w is not None
+            and x.dim() == 2 and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and w.dtype == x.dtype
+            and w.device == x.device and w.is_contiguous() and x.is_contiguous() and x.shape[1] % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 @_on_tensor_device

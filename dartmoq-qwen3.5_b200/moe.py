@@ -867,16 +867,38 @@ class WxA16BitPartitionedGroupMoE(nn.Module):
 
     def _body(self, eng, x, prof=None, partials=None):
         """Router, shared-expert gate and the expert path for x (T, H)."""
-        gate_out = self.gate(x)
-        if isinstance(gate_out, tuple):
+        shared_w = None
+        fuse_gate = False
+        if x.is_cuda and eng.has_shared and hasattr(self.gate, "router_logits"):
+            # a gate that can hand out its logits: softmax -> top-k (-> renormalise, as the gate says) and the shared
+            # expert's gate share one launch
+            from .kernels import fusable_shared_gate
+            fuse_gate = fusable_shared_gate(self.shared_expert_gate, x) and self.top_k <= 32
+        if fuse_gate:
+            from .kernels import router_topk
+            lg = self.gate.router_logits(x)
+            fuse_gate = lg.is_cuda and lg.shape[-1] <= 1024
+        if fuse_gate:
+            topk_w, topk_idx, shared_w = router_topk(lg.reshape(-1, lg.shape[-1]), self.top_k,
+                                                     renormalize=bool(getattr(self.gate, "norm_topk_prob", False)),
+                                                     x=x, shared_gate=self.shared_expert_gate)
+            gate_out = None
+        else:
+            gate_out = self.gate(x)
+        if gate_out is None:
+            pass
+        elif isinstance(gate_out, tuple):
             _, topk_w, topk_idx = gate_out
         elif gate_out.is_cuda and gate_out.shape[-1] <= 1024 and self.top_k <= 32:
-            from .kernels import router_topk
-            topk_w, topk_idx = router_topk(gate_out.reshape(-1, gate_out.shape[-1]), self.top_k)
+            from .kernels import fusable_shared_gate, router_topk
+            if eng.has_shared and fusable_shared_gate(self.shared_expert_gate, x):   # the gate rides in the router launch
+                topk_w, topk_idx, shared_w = router_topk(gate_out.reshape(-1, gate_out.shape[-1]), self.top_k,
+                                                         x=x, shared_gate=self.shared_expert_gate)
+            else:
+                topk_w, topk_idx = router_topk(gate_out.reshape(-1, gate_out.shape[-1]), self.top_k)
         else:
             topk_w, topk_idx = gate_out.softmax(dim=-1).topk(self.top_k, dim=-1)
-        shared_w = None
-        if eng.has_shared:
+        if eng.has_shared and shared_w is None:
             shared_w = torch.sigmoid(self.shared_expert_gate(x)).reshape(-1)
         if prof is not None:
             prof("router")

@@ -156,6 +156,18 @@ int dmoq_router_topk(const float* logits, int32_t T, int32_t E, int32_t top_k, i
                      float* topk_w, int64_t* topk_idx, void* stream);
 
 /*
+ * The same launch also computes the shared expert's gate of every token,
+ *   shared_w[t] = sigmoid(shared_expert_gate(x[t]))      (quantization/wxa16/bit_partitioned_moe.py:1101-1106),
+ * with the roundings of a 16-bit Linear(hidden, 1) and a 16-bit sigmoid: fp32 dot product of x[t] (bf16 when
+ * x_is_bf16, else fp16; rows of `hidden` elements, 16-byte aligned, hidden a multiple of 8) with gate_w (same type)
+ * plus gate_bias, rounded to that type, sigmoid in fp32, rounded again, stored as fp32 (the row weights
+ * dmoq_route_build takes for the shared expert).
+ */
+int dmoq_router_topk_gate(const float* logits, int32_t T, int32_t E, int32_t top_k, int32_t renormalize,
+                          float* topk_w, int64_t* topk_idx, const void* x, int32_t x_is_bf16, int32_t hidden,
+                          const void* gate_w, float gate_bias, float* shared_w, void* stream);
+
+/*
  * dmoq_route_build for callers that cannot allocate device memory (no counterpart in the reference,
  * whose routing runs as torch ops that allocate freely).  Who needs it: code that runs while a stream
  * is being captured, serving loops that froze their memory pools, host frameworks that own all

@@ -210,6 +210,27 @@ def test_router_topk_matches_torch(T, E, k, renorm):
     assert lib.dmoq_router_topk(_lib.ptr(logits), T, E, E + 1, 0, _lib.ptr(w), _lib.ptr(idx), None) == -1
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_router_launch_carries_shared_gate(dtype):
+    """sigmoid(shared_expert_gate(x)) from the router launch: the roundings of a 16-bit Linear + sigmoid; a value may
+    sit one 16-bit place from torch's where the two dot products (different summation order) round apart."""
+    T, H, E, k = 333, 512, 64, 4
+    g = torch.Generator().manual_seed(77)
+    logits = torch.randn(T, E, generator=g).to(DEV)
+    x = torch.randn(T, H, generator=g).to(dtype).to(DEV)
+    lin = torch.nn.Linear(H, 1, bias=False, dtype=dtype, device=DEV)
+    lin.weight.data.copy_((torch.randn(1, H, generator=g) * 0.05).to(dtype))
+    assert K.fusable_shared_gate(lin, x)
+    w, idx, sw = K.router_topk(logits, k, x=x, shared_gate=lin)
+    pw, pidx = torch.softmax(logits, dim=-1).topk(k, dim=-1)
+    assert torch.equal(idx, pidx) and torch.allclose(w, pw, rtol=2e-6, atol=1e-9)
+    want = torch.sigmoid(lin(x)).reshape(-1).float()
+    assert sw.dtype == torch.float32 and torch.equal(sw.to(dtype).float(), sw)       # values of the 16-bit type
+    assert (sw == want).float().mean() > 0.9
+    assert float((sw - want).abs().max()) <= (2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -9)
+    assert not K.fusable_shared_gate(torch.nn.Linear(H, 1, bias=True, dtype=dtype, device=DEV), x)
+
+
 @pytest.mark.parametrize("bit", [1, 2])
 def test_widen_indices(bit):
     """Every 1- or 2-bit code becomes one 4-bit field, low field first."""
