@@ -22,6 +22,7 @@ The reference has no counterpart (it has no distributed code).
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import List, Optional
 
 import numpy as np
@@ -125,7 +126,8 @@ class CodesExchange:
         self._pinned = None
         self._comm_stream = None
         self._pool_of = self._rank_of = None
-        self.n_chunks = 4               # blocks of each owner's experts the exchange is pipelined over
+        # blocks of each owner's experts the exchange is pipelined over (DMOQ_EP_CHUNKS overrides: tuning runs)
+        self.n_chunks = int(os.environ.get("DMOQ_EP_CHUNKS", "4"))
         self._owner_cap = 0
         self.last_stage_ms = None
         self.last_launches = 0

@@ -75,6 +75,26 @@ def test_static_scratch_route_matches_allocating_route_twice(T, k, E, shared):
         assert int(got["expert_rows"][-1]) == T * k + (T if shared else 0)
 
 
+def test_static_scratch_route_allocates_nothing():
+    """After a first call on the device, a further call leaves both the framework allocator's and the driver's
+    picture of device memory unchanged."""
+    lib = _lib.load()
+    T, k, E = 700, 4, 32
+    idx, w, sw, fresh, route = _tables(T, k, E, seed=5, has_shared=True)
+    out = fresh()
+    r = route(out)
+    for _ in range(2):                          # first call: one-time set-up of the library on this device
+        _lib.check(lib.dmoq_route_build_static(C.byref(r), _lib.ptr(idx), _lib.ptr(w), _lib.ptr(sw), None),
+                   "dmoq_route_build_static")
+    torch.cuda.synchronize()
+    before = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved(), torch.cuda.mem_get_info()[0])
+    _lib.check(lib.dmoq_route_build_static(C.byref(r), _lib.ptr(idx), _lib.ptr(w), _lib.ptr(sw), None),
+               "dmoq_route_build_static")
+    torch.cuda.synchronize()
+    after = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved(), torch.cuda.mem_get_info()[0])
+    assert before == after
+
+
 def test_static_scratch_route_refuses_oversized_problem():
     lib = _lib.load()
     T, k, E = 1 << 20, 8, 256                   # needs 8192 chunks x 256 experts x 4 B = 8 MiB > 4 MiB
