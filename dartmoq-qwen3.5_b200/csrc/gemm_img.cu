@@ -269,14 +269,6 @@ __device__ __forceinline__ void tc_mma_mxf4(uint32_t d_tmem, uint64_t a_desc, ui
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
       : "memory");
 }
-// accumulator loads: thread t of the warp receives lane base + t, register j = column base + j
-// 32 lanes x 8 columns
-__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t (&r)[8]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr)
-               : "memory");
-}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // 32 lanes x 4 columns: thread t writes its four values to lane base + t
@@ -359,7 +351,6 @@ __device__ __forceinline__ f32x2_t fma_x2(f32x2_t a, f32x2_t b, f32x2_t c) {
 
 // K-major, 128-byte swizzle: tile row r is 128 bytes; 16-byte chunk c lives at slot c ^ (r & 7); groups of 8 rows
 // are 1024 bytes apart (the descriptor's stride byte offset).  The TMA copy writes the same pattern.
-__device__ __forceinline__ uint32_t swz128(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
   return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
